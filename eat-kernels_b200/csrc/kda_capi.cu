@@ -1,0 +1,209 @@
+// extern "C" entry points of libkda_b200.so (declared in include/kda_b200.h).
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/kda_b200.h"
+#include "kda_common.cuh"
+#include "kda_cp.cuh"
+#include "kda_plan.cuh"
+
+namespace {
+
+thread_local char g_cuda_err[256] = "no CUDA error recorded";
+
+int cuda_fail(cudaError_t e) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "CUDA error %d: %s", (int)e, cudaGetErrorString(e));
+  return KDA_ERR_LAUNCH;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+struct Workspace {
+  kda::Task* tasks;
+  kda::Task* tasks_unsorted;
+  int* n_tasks;
+  long long* cu_safe;
+  float* trash;
+  size_t bytes;
+};
+
+Workspace carve(void* base, int N, int H) {
+  Workspace w;
+  size_t off = 0;
+  uint8_t* b = reinterpret_cast<uint8_t*>(base);
+  const size_t n = (size_t)(N > 0 ? N : 1);
+  w.tasks = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + n * sizeof(kda::Task), 256);
+  w.tasks_unsorted = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + n * sizeof(kda::Task), 256);
+  w.n_tasks = reinterpret_cast<int*>(b + off); off = align_up(off + 16, 256);
+  w.cu_safe = reinterpret_cast<long long*>(b + off); off = align_up(off + (n + 1) * sizeof(long long), 256);
+  w.trash = reinterpret_cast<float*>(b + off); off = align_up(off + (size_t)H * kda::STATE_ELEMS * sizeof(float), 256);
+  w.bytes = off;
+  return w;
+}
+
+int check_tokens(const KdaPrefillArgs* a) {
+  if (a == nullptr) return KDA_ERR_ARG;
+  if (a->H <= 0 || a->N < 0 || a->T < 0) return KDA_ERR_ARG;
+  if (a->frontend != KDA_FRONTEND_RAW && a->frontend != KDA_FRONTEND_PLAIN) return KDA_ERR_ARG;
+  if (a->state_layout != KDA_STATE_VALUE_FIRST && a->state_layout != KDA_STATE_KEY_FIRST) return KDA_ERR_ARG;
+  if (a->T > 0) {
+    if (!a->q || !a->k || !a->v || !a->g || !a->beta || !a->out) return KDA_ERR_ARG;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->g) || !aligned16(a->out)) return KDA_ERR_ARG;
+    const int64_t hd = (int64_t)a->H * KDA_HEAD_DIM;
+    if (a->ldq < hd || a->ldk < hd || a->ldv < hd || a->ldg < hd || a->ldo < hd || a->ldbeta < a->H) return KDA_ERR_ARG;
+    if ((a->ldq | a->ldk | a->ldv | a->ldo) & 7) return KDA_ERR_ARG;
+    if (a->ldg & (a->frontend == KDA_FRONTEND_PLAIN ? 3 : 7)) return KDA_ERR_ARG;
+  }
+  if (a->frontend == KDA_FRONTEND_RAW && (!a->A_log || !a->dt_bias)) return KDA_ERR_ARG;
+  if (!a->status || !a->workspace) return KDA_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return KDA_ERR_ARG;
+  return KDA_OK;
+}
+
+void fill_chunk_params(kda::ChunkParams& p, const KdaPrefillArgs* a) {
+  memset(&p, 0, sizeof(p));
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
+  p.k = reinterpret_cast<const __nv_bfloat16*>(a->k);
+  p.v = reinterpret_cast<const __nv_bfloat16*>(a->v);
+  p.g = a->g;
+  p.beta = a->beta;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  p.out_aux = nullptr;
+  p.ldq = a->ldq; p.ldk = a->ldk; p.ldv = a->ldv; p.ldg = a->ldg; p.ldbeta = a->ldbeta; p.ldo = a->ldo;
+  p.A_log = a->A_log;
+  p.dt_bias = a->dt_bias;
+  p.scale = a->scale;
+  p.lower_bound = a->lower_bound;
+  p.frontend = a->frontend;
+  p.key_first = a->state_layout == KDA_STATE_KEY_FIRST;
+  p.H = a->H;
+  p.T = a->T;
+  p.status = a->status;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t kda_prefill_workspace_bytes(int32_t N, int32_t H) {
+  if (N < 0 || H <= 0) return 0;
+  return carve(nullptr, N, H).bytes;
+}
+
+int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = check_tokens(a);
+  if (rc != KDA_OK) return rc;
+  if (a->N < 1) return KDA_ERR_ARG;
+  if (a->cu_seqlens == nullptr && a->N != 1) return KDA_ERR_ARG;
+  if (a->ck_every != 0) {
+    if (a->ck_every < 0 || a->ck_every % KDA_CHUNK) return KDA_ERR_ARG;
+    if (!a->ck_base || !a->ck_starts || a->ck_rows < 0) return KDA_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(a->ck_base) & 7) return KDA_ERR_ARG;
+  }
+  if (a->src_base && (!aligned16(a->src_base) || (a->src_slot_stride & 3))) return KDA_ERR_ARG;
+  if (a->dst_base && (!aligned16(a->dst_base) || (a->dst_slot_stride & 3))) return KDA_ERR_ARG;
+  const Workspace w = carve(a->workspace, a->N, a->H);
+  if (a->workspace_bytes < w.bytes) return KDA_ERR_WORKSPACE;
+
+  kda::PlanParams pl;
+  memset(&pl, 0, sizeof(pl));
+  pl.N = a->N; pl.H = a->H; pl.T = a->T;
+  pl.cu = a->cu_seqlens; pl.cu_is64 = a->cu_is64;
+  pl.src_base = a->src_base; pl.src_stride = a->src_slot_stride; pl.src_idx = a->src_idx; pl.src_is64 = a->src_idx_is64;
+  pl.src_slots = a->src_slots;
+  pl.src_separate = !(a->src_base != nullptr && a->src_base == a->dst_base && a->dst_idx != nullptr && a->src_idx == nullptr);
+  pl.dst_base = a->dst_base; pl.dst_stride = a->dst_slot_stride; pl.dst_idx = a->dst_idx; pl.dst_is64 = a->dst_idx_is64;
+  pl.dst_slots = a->dst_slots;
+  pl.ck_base = a->ck_every ? a->ck_base : nullptr; pl.ck_is_bf16 = a->ck_is_bf16; pl.ck_every = a->ck_every;
+  pl.ck_rows = a->ck_rows; pl.ck_row_stride = (long long)a->H * kda::STATE_ELEMS;
+  pl.ck_starts = a->ck_starts; pl.ck_is64 = a->ck_starts_is64;
+  pl.trash = w.trash; pl.cu_safe = w.cu_safe; pl.tasks_unsorted = w.tasks_unsorted; pl.tasks = w.tasks;
+  pl.n_tasks = w.n_tasks; pl.status = a->status;
+  cudaError_t e = kda::launch_plan(pl, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+
+  kda::ChunkParams p;
+  fill_chunk_params(p, a);
+  p.ck_is_bf16 = a->ck_is_bf16;
+  p.ck_every_chunks = a->ck_every / KDA_CHUNK;
+  p.ck_row_stride = (long long)a->H * kda::STATE_ELEMS;
+  p.tasks = w.tasks;
+  p.n_tasks = w.n_tasks;
+  e = kda::launch_chunk_fwd(p, a->N, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return KDA_OK;
+}
+
+int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (s == nullptr) return KDA_ERR_ARG;
+  const KdaPrefillArgs* a = &s->base;
+  int rc = check_tokens(a);
+  if (rc != KDA_OK) return rc;
+  if (s->n_seg < 1 || !s->seg_t0 || !s->seg_t1 || !s->seg_need_map || !s->S_loc) return KDA_ERR_ARG;
+  const Workspace w = carve(a->workspace, 2 * s->n_seg, a->H);
+  if (a->workspace_bytes < w.bytes) return KDA_ERR_WORKSPACE;
+  kda::SegPlanParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.n_seg = s->n_seg; sp.H = a->H; sp.T = a->T;
+  sp.t0 = reinterpret_cast<const long long*>(s->seg_t0); sp.t1 = reinterpret_cast<const long long*>(s->seg_t1);
+  sp.need_map = s->seg_need_map;
+  sp.src_base = a->src_base; sp.src_stride = a->src_slot_stride;
+  sp.P = s->P; sp.S_loc = s->S_loc;
+  sp.tasks = w.tasks; sp.n_tasks = w.n_tasks; sp.status = a->status;
+  cudaError_t e = kda::launch_seg_plan(sp, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  kda::ChunkParams p;
+  fill_chunk_params(p, a);
+  p.out_aux = reinterpret_cast<__nv_bfloat16*>(s->qt);
+  p.key_first = 0;
+  p.tasks = w.tasks;
+  p.n_tasks = w.n_tasks;
+  e = kda::launch_chunk_fwd(p, 2 * s->n_seg, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return KDA_OK;
+}
+
+int kda_scan_launch(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int32_t n_seg,
+                    int32_t H, void* stream_) {
+  if (!P || !S_loc || !S_in || n_seg < 1 || H < 1) return KDA_ERR_ARG;
+  cudaError_t e = kda::launch_scan(P, S_loc, S0, S_in, S_end, n_seg, H, reinterpret_cast<cudaStream_t>(stream_));
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
+
+int kda_fixup_launch(void* out, const void* qt, int64_t ldo, const float* S_in, const int64_t* seg_t0,
+                     const int64_t* seg_t1, const int32_t* seg_need_map, int32_t n_seg, int32_t H, void* stream_) {
+  if (!out || !qt || !S_in || !seg_t0 || !seg_t1 || !seg_need_map || n_seg < 1 || H < 1) return KDA_ERR_ARG;
+  if (!aligned16(out) || !aligned16(qt) || (ldo & 7) || ldo < (int64_t)H * KDA_HEAD_DIM) return KDA_ERR_ARG;
+  cudaError_t e = kda::launch_fixup(reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(qt), ldo,
+                                    S_in, reinterpret_cast<const long long*>(seg_t0), reinterpret_cast<const long long*>(seg_t1),
+                                    seg_need_map, n_seg, H, reinterpret_cast<cudaStream_t>(stream_));
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
+
+int kda_state_rows_copy(void* dst, int64_t dst_row_stride, int32_t dst_is_bf16, const float* src,
+                        int64_t src_row_stride, const int32_t* idx, int32_t n_rows, int32_t H, void* stream_) {
+  if (!dst || !src || n_rows < 0 || H < 1) return KDA_ERR_ARG;
+  if (!aligned16(dst) || !aligned16(src) || (dst_row_stride & 7) || (src_row_stride & 3)) return KDA_ERR_ARG;
+  if (n_rows == 0) return KDA_OK;
+  cudaError_t e = kda::launch_rows_copy(dst, dst_row_stride, dst_is_bf16, src, src_row_stride, idx, n_rows, H,
+                                        reinterpret_cast<cudaStream_t>(stream_));
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
+
+const char* kda_error_string(int code) {
+  switch (code) {
+    case KDA_OK: return "ok";
+    case KDA_ERR_ARG: return "invalid argument (null or misaligned pointer, bad stride or size)";
+    case KDA_ERR_WORKSPACE: return "workspace too small";
+    case KDA_ERR_LAUNCH: return g_cuda_err;
+    case KDA_ERR_LIMIT: return "size beyond a documented maximum";
+    default: return "unknown error code";
+  }
+}
+
+const char* kda_version(void) { return "kda_b200 1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,29 @@
+// Context-parallel helpers: segment task planning, state-map scan, output fix-up, state row copies (see kda_cp.cu).
+#pragma once
+#include "kda_common.cuh"
+
+namespace kda {
+
+struct SegPlanParams {
+  int n_seg, H;
+  long long T;
+  const long long* t0;
+  const long long* t1;
+  const int* need_map;
+  const float* src_base; long long src_stride;
+  float* P;
+  float* S_loc;
+  Task* tasks;     // [2 * n_seg]
+  int* n_tasks;
+  int* status;
+};
+
+cudaError_t launch_seg_plan(const SegPlanParams& a, cudaStream_t stream);
+cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int n_seg, int H,
+                        cudaStream_t stream);
+cudaError_t launch_fixup(__nv_bfloat16* out, const __nv_bfloat16* qt, long long ldo, const float* S_in, const long long* t0,
+                         const long long* t1, const int* need_map, int n_seg, int H, cudaStream_t stream);
+cudaError_t launch_rows_copy(void* dst, long long dst_row_stride, int dst_is_bf16, const float* src, long long src_row_stride,
+                             const int* idx, int n_rows, int H, cudaStream_t stream);
+
+}  // namespace kda
