@@ -204,6 +204,8 @@ const char* kda_error_string(int code) {
   }
 }
 
+size_t kda_abi_struct_bytes(int which) { return which == 0 ? sizeof(KdaPrefillArgs) : (which == 1 ? sizeof(KdaSegmentArgs) : 0); }
+
 const char* kda_version(void) { return "kda_b200 1 sm_100a"; }
 
 }  // extern "C"

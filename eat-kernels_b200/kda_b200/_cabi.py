@@ -11,7 +11,7 @@ LIB_PATH = PKG / "libkda_b200.so"
 FRONTEND_RAW, FRONTEND_PLAIN = 0, 1
 STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
 EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_segment_launch", "kda_scan_launch",
-           "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_version"]
+           "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version"]
 
 
 class KdaPrefillArgs(C.Structure):
@@ -74,6 +74,10 @@ def lib():
         L.kda_error_string.argtypes = [C.c_int]
         L.kda_error_string.restype = C.c_char_p
         L.kda_version.restype = C.c_char_p
+        L.kda_abi_struct_bytes.argtypes = [C.c_int]
+        L.kda_abi_struct_bytes.restype = C.c_size_t
+        if (L.kda_abi_struct_bytes(0) != C.sizeof(KdaPrefillArgs) or L.kda_abi_struct_bytes(1) != C.sizeof(KdaSegmentArgs)):
+            raise RuntimeError("libkda_b200.so and the Python binding disagree on the argument struct layout: rebuild")
         _lib = L
     return _lib
 

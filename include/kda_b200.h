@@ -151,6 +151,10 @@ int kda_state_rows_copy(void* dst, int64_t dst_row_stride, int32_t dst_is_bf16, 
 /* Text of a KDA_ERR_* code; for KDA_ERR_LAUNCH the last CUDA error string seen by this thread. */
 const char* kda_error_string(int code);
 
+/* sizeof(KdaPrefillArgs) (which = 0) or sizeof(KdaSegmentArgs) (which = 1) as the library was compiled: lets a foreign
+ * binding check its struct layout before the first call. */
+size_t kda_abi_struct_bytes(int which);
+
 /* Library version and build information ("kda_b200 <n> sm_100a"). */
 const char* kda_version(void);
 
