@@ -1,0 +1,310 @@
+#!/usr/bin/env python3
+"""KDA prefill benchmark on B200: tokens/s of the serving call (H = 64, K = V = 128, varlen) at 1/2/4/8 GPUs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # N > 1: launched by torch.distributed.run
+    python bench.py --impl reference ...                            # the CPU restatement of the reference's definition
+
+Workload (BASELINE.json configs[2], the H = 64 varlen serving configuration the metric is quoted on): a paged fp32
+state pool of 256 slots, 48 requests on random distinct slots, new-token lengths lognormal(ln 1024, 0.8) clipped to
+[16, 8192], bf16 checkpoints every 1024 tokens, pre-activated inputs (bf16 q/k/v, fp32 log-decay g and beta).
+Synthetic seeded data.  With N GPUs the 64 heads are sharded N ways (no collective on the data path: strong scaling).
+
+A step is one prefill call (device planner + fused chunk kernel) over the whole batch.  Inputs (several GB) are far
+larger than L2, so every step streams them from HBM.  Timing: CUDA events on the launching stream, barrier +
+synchronize on both sides, max over ranks.  One JSON line on stdout from rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "eat-kernels_b200"))
+
+D = 128
+H_TOTAL = 64
+N_REQ = 48
+POOL_SLOTS = 256
+CK_EVERY = 1024
+FLOP_PER_TOKEN_HEAD = 6 * D * D + 4 * 64 * (D + D)          # 163 840, canonical chunk 64
+BYTES_PER_TOKEN_HEAD = 3 * D * 2 + D * 4 + 4 + D * 2         # q,k,v bf16 + g fp32 + beta fp32 + out bf16 = 1540
+METRIC = "KDA prefill tokens/s (H=64,K=V=128 varlen)"
+# dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_fwd_kernel per token-head, from the ncu capture of
+# `bench.py --small` summarised under profiles/ (traffic grows in proportion to token-heads); None until captured.
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = None
+
+
+def workload_lengths(seed=2):
+    gen = torch.Generator().manual_seed(seed)
+    ln = torch.exp(torch.randn(N_REQ, generator=gen) * 0.8 + math.log(1024.0))
+    return [int(x) for x in ln.clamp(16, 8192).round().tolist()]
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return {"hbm_gbs": float(j["hbm_gbs"]), "tf": float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tf": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(",") for r in Path(self.f.name).read_text().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_device_inputs(H, lens, seed, dev):
+    """Pre-activated inputs of the head shard on the device: q, k normalised then bf16, v bf16, g = logsigmoid(N(0,1))
+    fp32, beta = sigmoid(N(0,1)) fp32."""
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    T = sum(lens)
+    q = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    v = torch.randn(1, T, H, D, generator=gen, device=dev).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=dev))
+    beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=dev))
+    return q, k, v, g, beta
+
+
+def cpu_baseline(lens, H, target_s=12.0):
+    """The oracle's C restatement of the reference recurrence (fp32 working precision, OpenMP over sequence-heads) on
+    a bounded prefix of the same workload; returns the cpu_baseline object."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import c_oracle
+    import kda_oracle as ko
+    threads = c_oracle.threads("f32")
+
+    def run(n_tok):
+        sample_lens, left = [], n_tok
+        for L in lens:
+            if left <= 0:
+                break
+            sample_lens.append(min(L, left)); left -= sample_lens[-1]
+        q, k, v, g, beta, scale, init, cu = ko.make_inputs_plain(H, sample_lens, 5)
+        t = time.perf_counter()
+        c_oracle.recurrence_plain(q, k, v, g, beta, scale, init, cu, precision="f32")
+        return sum(sample_lens), time.perf_counter() - t, len(sample_lens)
+
+    run(64)                                            # touch the library
+    n0, t0, _ = run(256)
+    n_tok = int(min(sum(lens), max(256, 256 * target_s / max(t0, 1e-3))))
+    n, t, nseq = run(n_tok)
+    return {"value": n / t, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"first {n} tokens ({nseq} sequences) of the workload at H={H}, fp32 C restatement of "
+                      f"kda/b200/reference.py, {threads} OpenMP threads of {os.cpu_count()} host CPUs, {t:.1f} s"}, n, t
+
+
+def run_reference(args, lens):
+    """--impl reference: the CPU implementation of the path (oracle port: the reference's own CPU code is Python and
+    its CUDA path needs a GPU build) timed per step on a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    base, n, t = cpu_baseline(lens, H_TOTAL, target_s=3.0)
+    times = []
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import c_oracle
+    import kda_oracle as ko
+    sample_lens, left = [], n
+    for L in lens:
+        if left <= 0:
+            break
+        sample_lens.append(min(L, left)); left -= sample_lens[-1]
+    q, k, v, g, beta, scale, init, cu = ko.make_inputs_plain(H_TOTAL, sample_lens, 5)
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        c_oracle.recurrence_plain(q, k, v, g, beta, scale, init, cu, precision="f32")
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    value = n / sec
+    base["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "configs[2] serving call H=64 K=V=128, 48 requests lognormal lengths; CPU arm runs "
+                                   f"a prefix of {n} tokens per step", "heads": H_TOTAL},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+    return 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
+    args = ap.parse_args(argv)
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    lens = workload_lengths()
+    if args.small:
+        lens = lens[:8]
+    if args.impl == "reference":
+        return run_reference(args, lens)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import kda_b200
+
+    assert H_TOTAL % world == 0
+    H = H_TOTAL // world
+    T, N = sum(lens), len(lens)
+    q, k, v, g, beta = make_device_inputs(H, lens, 100 + rank, dev)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    pool = torch.randn(POOL_SLOTS, H, D, D, generator=gen, device=dev) * 0.05
+    slots = torch.randperm(POOL_SLOTS, generator=torch.Generator().manual_seed(3))[:N].to(torch.int32).to(dev)
+    cu = torch.tensor([0, *torch.tensor(lens).cumsum(0).tolist()], dtype=torch.int64, device=dev)
+    counts = [-(-n // CK_EVERY) for n in lens]
+    ck_starts = torch.tensor([0, *torch.tensor(counts).cumsum(0).tolist()], dtype=torch.int64, device=dev)
+    rows = sum(counts)
+    ck = torch.zeros(rows, H, D, D, dtype=torch.bfloat16, device=dev)
+    launch = kda_b200.prepare_plain(q, k, v, g, beta, D ** -0.5, pool, False, cu, dynamic_layout=True,
+                                    ssm_state_indices=slots, state_checkpoints=ck, checkpoint_cu_starts=ck_starts,
+                                    checkpoint_every_n_tokens=CK_EVERY)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        launch()
+    barrier()
+    if kda_b200.status_bits(launch) != 0 or kda_b200.kernel_error(launch) != 0:
+        raise SystemExit("bench: the launch reported a table or kernel error")
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        launch()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end to end through the public call with HOST buffers: pinned inputs -> device -> prefill -> output to host
+    e2e = None
+    if args.e2e_steps > 0:
+        host = [t.cpu().pin_memory() for t in (q, k, v, g, beta, cu, slots, ck_starts)]
+        devs = [q, k, v, g, beta, cu, slots, ck_starts]
+        out_host = torch.empty((1, T, H, D), dtype=torch.bfloat16).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        d2h = out_host.numel() * out_host.element_size()
+
+        def step():
+            for d_, h_ in zip(devs, host):
+                d_.copy_(h_, non_blocking=True)
+            res = launch()
+            out_host.copy_(res[0], non_blocking=True)
+
+        step()
+        barrier()
+        e0.record()
+        for _ in range(args.e2e_steps):
+            step()
+        e1.record()
+        barrier()
+        ems = e0.elapsed_time(e1) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([ems], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = float(t.item())
+        e2e = {"value": T / (ems * 1e-3), "unit": "tokens/s", "ms_per_step": ems, "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h * world}
+
+    if rank == 0:
+        pk = peaks()
+        algo_bytes = T * H * BYTES_PER_TOKEN_HEAD + N * H * 2 * D * D * 4 + rows * H * D * D * 2
+        achieved = algo_bytes / (ms * 1e-3) / 1e9
+        flops = T * H * FLOP_PER_TOKEN_HEAD
+        tf = flops / (ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[2]: serving call, H=64 (sharded by heads over the GPUs), K=V=128, 48 requests, "
+                                   "lengths lognormal(ln1024,0.8) clipped [16,8192], fp32 pool of 256 slots, bf16 checkpoints "
+                                   "every 1024 tokens, pre-activated bf16 q/k/v + fp32 g/beta" + (" [--small]" if args.small else ""),
+                       "tokens": T, "requests": N, "heads_per_gpu": H, "checkpoint_rows": rows,
+                       "l2": "inputs (GBs per step) far exceed L2; no flush needed", "parallelism": f"hp{world}"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],
+                         "kernel": "kda_chunk_fwd_kernel (the step also holds the planner kernel, < 1 % of the time)",
+                         "algorithmic_bytes_per_launch": algo_bytes},
+            "tensor": {"achieved": tf, "peak": pk["tf"], "unit": "TFLOP/s", "frac": tf / pk["tf"],
+                       "flops_per_launch": flops, "note": "dense count 163840 FLOP per token-head (chunk 64 convention)"},
+            "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks,
+        }
+        if NCU_DRAM_BYTES_PER_TOKEN_HEAD is not None:
+            line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_TOKEN_HEAD * T * H
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _, _ = cpu_baseline(lens, H_TOTAL)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
