@@ -45,6 +45,7 @@ Workspace carve(void* base, int N, int H) {
 int check_tokens(const KdaPrefillArgs* a) {
   if (a == nullptr) return KDA_ERR_ARG;
   if (a->H <= 0 || a->N < 0 || a->T < 0) return KDA_ERR_ARG;
+  if (a->kernel != KDA_KERNEL_TCGEN05 && a->kernel != KDA_KERNEL_MMA_SYNC) return KDA_ERR_ARG;
   if (a->frontend != KDA_FRONTEND_RAW && a->frontend != KDA_FRONTEND_PLAIN) return KDA_ERR_ARG;
   if (a->state_layout != KDA_STATE_VALUE_FIRST && a->state_layout != KDA_STATE_KEY_FIRST) return KDA_ERR_ARG;
   if (a->T > 0) {
@@ -131,7 +132,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   p.ck_row_stride = (long long)a->H * kda::STATE_ELEMS;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
-  e = kda::launch_chunk_fwd(p, a->N, stream);
+  e = a->kernel == KDA_KERNEL_MMA_SYNC ? kda::launch_chunk_fwd(p, a->N, stream) : kda::launch_chunk_umma(p, a->N, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;
 }
@@ -161,7 +162,8 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   p.key_first = 0;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
-  e = kda::launch_chunk_fwd(p, 2 * s->n_seg, stream);
+  e = a->kernel == KDA_KERNEL_MMA_SYNC ? kda::launch_chunk_fwd(p, 2 * s->n_seg, stream)
+                                       : kda::launch_chunk_umma(p, 2 * s->n_seg, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;
 }

@@ -1,0 +1,687 @@
+// Fused KDA chunk kernel on the 5th-generation tensor core (tcgen05 + tensor memory), sm_100a.
+//
+// One CTA walks the 32-token chunks of one (token run, head) task.  The fp32 state St [V=128][K=128] (value-first) never
+// leaves tensor memory between chunks, and the whole per-chunk chain is tensor-core work issued by one thread:
+//
+//   MMA1  [W | O] = St [kd ; qd]^T          tf32: A = St read straight from its accumulator columns, N = 64, K = 128
+//   MMA2  U  = v^T Tbh^T - W Tb^T           bf16 (A = v tile, MN-major) then tf32 (A = W columns, B negated), N = 32, K = 32
+//   MMA3  St += U kr ,  O += U M^T          tf32: A = U columns; kr MN-major (N = 128), M K-major (N = 32)
+//
+// with kd = k 2^G, qd = scale q 2^G, kr = k 2^(G31-G), Tb = (I + diag(beta) tril(kd' ki'^T,-1))^-1 diag(beta),
+// M = tril(qd' ki'^T) (G = inclusive cumulative log2-decay of the chunk; primed operands are taken relative to the
+// exponent after token 15 so that every exponent is bounded by the decay of 16 tokens).  This is the chunked form of
+// kda/b200/reference.py:30-37.  No accumulator makes a round trip through registers on the chain; the only register
+// pass is the per-chunk decay St <- St diag(2^G31), done by four "scaler" warps between MMA1 and MMA3, off the MMA
+// thread's issue path.  Because tf32 operands keep 10 mantissa bits, the state enters the products more accurately
+// than a bf16 copy would.
+//
+// Warp roles (20 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
+// 3 loader (cp.async of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
+// checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-19 operand preparation (gate + cumsum, L2 norm,
+// decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
+// (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
+// code in status[2].
+#include "kda_common.cuh"
+#include "kda_plan.cuh"
+#include "kda_umma.cuh"
+
+namespace kda {
+using namespace umma;
+
+namespace u {
+
+constexpr int WARPS = 20;
+constexpr int THREADS = WARPS * 32;
+constexpr int W_MMA = 0, W_INV0 = 1, W_LOAD = 3, W_SCALE0 = 4, W_EPI0 = 8, W_PREP0 = 12;
+constexpr int PREP_WARPS = 8, PREP_THREADS = 256;
+
+// ---- shared memory map (bytes); operand tiles are 1024-byte aligned
+constexpr int CS_KDQD = 0, CS_KR = 32768, CS_V = 49152, CS_TB = 57344, CS_M = 61440, CS_STAGE = 65536;
+constexpr int OFF_CONS = 0;                                   // 2 stages
+constexpr int RAW_G = 0, RAW_Q = 16384, RAW_K = 24576, RAW_STAGE = 32768;
+constexpr int OFF_RAW = OFF_CONS + 2 * CS_STAGE;              // 2 stages
+constexpr int OFF_KIS = OFF_RAW + 2 * RAW_STAGE;              // 8192
+constexpr int OFF_TBH = OFF_KIS + 8192;                       // 2 x 2048 (bf16, 64-byte swizzle)
+constexpr int OFF_L = OFF_TBH + 4096;                         // 2 x 4096 fp32 [32][32]
+constexpr int OFF_DEC = OFF_L + 8192;                         // 2 x 512
+constexpr int OFF_FR = OFF_DEC + 1024;                        // r, 2^r : 2 x 512
+constexpr int OFF_TOT = OFF_FR + 1024;                        // 512
+constexpr int OFF_BETA = OFF_TOT + 512;                       // raw-stage beta: 2 x 128
+constexpr int OFF_LBETA = OFF_BETA + 256;                     // beta next to L: 2 x 128
+constexpr int OFF_BAR = OFF_LBETA + 256;                      // mbarriers
+constexpr int NUM_BARS = 24;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem slot, abort flag
+constexpr int SMEM_BYTES = OFF_MISC + 64;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+// mbarrier indices
+constexpr int B_RAW_FULL = 0, B_RAW_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
+              B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20;
+
+// tensor-memory columns
+constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
+
+// error codes written to status[2] when a bounded wait gives up (which role, which barrier)
+constexpr int E_LOAD = 0x10, E_PREP = 0x20, E_INV = 0x30, E_MMA = 0x40, E_SCALE = 0x50, E_EPI = 0x60;
+
+#ifdef KDA_PROF
+#define PROF_STAMP(role, slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(x.prof + (role) * 32 + (slot), (unsigned long long)(_t - prof_last)); prof_last = _t; } } while (0)
+#define PROF_BEGIN long long prof_last = clock64()
+#else
+#define PROF_STAMP(role, slot) do { } while (0)
+#define PROF_BEGIN do { } while (0)
+#endif
+
+struct Ctx {
+  uint8_t* smem;
+  uint32_t bars;              // shared address of barrier 0
+  volatile int* abort_flag;
+  int h, len, nchunks;
+  long long t0;
+  __device__ __forceinline__ uint32_t bar(int i) const { return bars + 8u * (uint32_t)i; }
+#ifdef KDA_PROF
+  unsigned long long* prof;   // [role 0..7][barrier 0..23 | 24 = total] cycle counters of CTA 0 (profiling builds only)
+  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const {
+    const long long t = clock64();
+    mbar_wait(bar(i), parity, abort_flag, code + i);
+    if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 32 + i), (unsigned long long)(clock64() - t));
+  }
+#else
+  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
+#endif
+  // for a single elected thread (the MMA issuer)
+  __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
+};
+
+// ------------------------------------------------------------------------------------------------ loader warp
+__device__ __forceinline__ void loader_issue(const ChunkParams& p, const Ctx& x, int c, int lane) {
+  const int rs = c & 1;
+  const int nvalid = min(C, x.len - c * C);
+  const long long tok0 = x.t0 + (long long)c * C;
+  uint8_t* raw = x.smem + OFF_RAW + rs * RAW_STAGE;
+  const uint32_t graw = smem_u32(raw + RAW_G), qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
+  const uint32_t vdst = smem_u32(x.smem + OFF_CONS + rs * CS_STAGE + CS_V);
+  if (p.frontend == 1) {
+    const float* g = reinterpret_cast<const float*>(p.g);
+#pragma unroll 4
+    for (int j = 0; j < 32; j++) {
+      const int idx = lane + 32 * j, row = idx >> 5, ch = idx & 31;
+      const bool ok = row < nvalid;
+      cp_async16(graw + row * 512 + ch * 16, g + (tok0 + (ok ? row : 0)) * p.ldg + (long long)x.h * D + ch * 4, ok ? 16 : 0);
+    }
+  } else {
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.g);
+#pragma unroll 4
+    for (int j = 0; j < 16; j++) {
+      const int idx = lane + 32 * j, row = idx >> 4, ch = idx & 15;
+      const bool ok = row < nvalid;
+      cp_async16(graw + row * 256 + ch * 16, g + (tok0 + (ok ? row : 0)) * p.ldg + (long long)x.h * D + ch * 8, ok ? 16 : 0);
+    }
+  }
+#pragma unroll 4
+  for (int j = 0; j < 16; j++) {
+    const int idx = lane + 32 * j, row = idx >> 4, ch = idx & 15;
+    const bool ok = row < nvalid;
+    const long long tok = tok0 + (ok ? row : 0);
+    const int n = ok ? 16 : 0;
+    const uint32_t sw = (uint32_t)(row * 256 + ((ch ^ (row & 7)) << 4));
+    cp_async16(qraw + sw, p.q + tok * p.ldq + (long long)x.h * D + ch * 8, n);
+    cp_async16(kraw + sw, p.k + tok * p.ldk + (long long)x.h * D + ch * 8, n);
+    // v: A operand of MMA2 (M = value index, K = token), MN-major, 64 values per 128-byte row
+    cp_async16(vdst + mnmajor_b16_off(ch * 8, row, 4096, 1024), p.v + tok * p.ldv + (long long)x.h * D + ch * 8, n);
+  }
+}
+
+__device__ __forceinline__ float load_beta(const ChunkParams& p, const Ctx& x, int c, int row) {
+  const int nvalid = min(C, x.len - c * C);
+  if (row >= nvalid) return 0.0f;
+  const long long tok = x.t0 + (long long)c * C + row;
+  if (p.frontend == 1) return reinterpret_cast<const float*>(p.beta)[tok * p.ldbeta + x.h];
+  return sigmoidf_rel(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[tok * p.ldbeta + x.h]));
+}
+
+__device__ void role_loader(const ChunkParams& p, const Ctx& x, int lane, bool v_zero) {
+  float beta_next = x.nchunks > 0 ? load_beta(p, x, 0, lane) : 0.0f;
+  for (int c = 0; c < x.nchunks; c++) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    x.wait(B_RAW_EMPTY + s, par ^ 1, E_LOAD);
+    x.wait(B_CONS_EMPTY + s, par ^ 1, E_LOAD);
+    PROF_BEGIN;
+    loader_issue(p, x, c, lane);
+    PROF_STAMP(1, 26);
+    reinterpret_cast<float*>(x.smem + OFF_BETA)[s * 32 + lane] = beta_next;
+    if (c + 1 < x.nchunks) beta_next = load_beta(p, x, c + 1, lane);
+    cp_async_commit();
+    PROF_STAMP(1, 27);
+    if (c > 0) {
+      cp_async_wait<1>();
+      PROF_STAMP(1, 28);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x.bar(B_RAW_FULL + ((c - 1) & 1)));
+    }
+  }
+  if (x.nchunks > 0) {
+    cp_async_wait<0>();
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(x.bar(B_RAW_FULL + ((x.nchunks - 1) & 1)));
+  }
+  (void)v_zero;
+}
+
+// ------------------------------------------------------------------------------------------------ prep warps
+__device__ __forceinline__ void prep_bar() { named_bar_sync(1, PREP_THREADS); }
+
+__device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_zero) {
+  const int pw = ptid >> 5, lane = ptid & 31;
+  const int ch = ptid & 127, half = ptid >> 7;
+  float eA = 0.0f, dtb = 0.0f;
+  if (p.frontend == 0) {
+    eA = __expf(p.A_log[x.h]);
+    dtb = p.dt_bias[x.h * D + ch];
+  }
+  float* fr = reinterpret_cast<float*>(x.smem + OFF_FR);
+  float* fer = fr + D;
+  float* tot = reinterpret_cast<float*>(x.smem + OFF_TOT);
+  for (int c = 0; c < x.nchunks; c++) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    const int nvalid = min(C, x.len - c * C);
+    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+    uint8_t* cons = x.smem + OFF_CONS + s * CS_STAGE;
+    float* Gsm = reinterpret_cast<float*>(raw + RAW_G);
+    float* dec = reinterpret_cast<float*>(x.smem + OFF_DEC) + s * D;
+    x.wait(B_RAW_FULL + s, par, E_PREP);
+    x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
+    PROF_BEGIN;
+
+    // ---- A: gate activation + inclusive cumulative log2-decay; two threads per channel, 16 tokens each
+    {
+      float a[16];
+      if (p.frontend == 1) {
+        const float* g = reinterpret_cast<const float*>(raw + RAW_G);
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] = g[(16 * half + i) * D + ch] * LOG2E;
+      } else {
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(raw + RAW_G);
+        const float c2 = p.lower_bound * LOG2E;
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] = c2 * sigmoidf_rel(eA * (__bfloat162float(g[(16 * half + i) * D + ch]) + dtb));
+      }
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        if (16 * half + i >= nvalid) a[i] = 0.0f;
+        if (i > 0) a[i] += a[i - 1];
+      }
+      if (half == 0) tot[ch] = a[15];
+      prep_bar();                       // all raw g values are in registers: G may now overwrite them in place
+      if (half == 1) {
+        const float r = tot[ch];
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] += r;
+        fr[ch] = r;
+        fer[ch] = ex2f(r);
+        dec[ch] = ex2f(a[15]);
+        tot[ch] = ex2f(a[15] - r);      // 2^(G31 - r), read back below as the kr factor
+      }
+#pragma unroll
+      for (int i = 0; i < 16; i++) Gsm[(16 * half + i) * D + ch] = a[i];
+    }
+    prep_bar();
+    PROF_STAMP(2, 26);
+
+    // ---- B: L2 norm and decayed operand tiles; a warp owns 4 tokens, a lane 4 channels
+    {
+      const float4 r4 = *reinterpret_cast<const float4*>(fr + 4 * lane);
+      const float4 er4 = *reinterpret_cast<const float4*>(fer + 4 * lane);
+      const float4 elr4 = *reinterpret_cast<const float4*>(tot + 4 * lane);
+      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
+      const float er[4] = {er4.x, er4.y, er4.z, er4.w};
+      const float elr[4] = {elr4.x, elr4.y, elr4.z, elr4.w};
+#pragma unroll
+      for (int tt = 0; tt < 4; tt++) {
+        const int tok = 4 * pw + tt;
+        const uint32_t off = tile128_off(tok, 4 * lane);
+        const uint2 q2 = *reinterpret_cast<const uint2*>(raw + RAW_Q + off);
+        const uint2 k2 = *reinterpret_cast<const uint2*>(raw + RAW_K + off);
+        const float qf[4] = {bf16_lo(q2.x), bf16_hi(q2.x), bf16_lo(q2.y), bf16_hi(q2.y)};
+        const float kf[4] = {bf16_lo(k2.x), bf16_hi(k2.x), bf16_lo(k2.y), bf16_hi(k2.y)};
+        float qinv = p.scale, kinv = 1.0f;
+        if (p.frontend == 0) {
+          float sq = qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3];
+          float sk = kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+          }
+          qinv = p.scale * rsqrtf(fmaxf(sq, 1e-12f));   // x / max(||x||, 1e-6)
+          kinv = rsqrtf(fmaxf(sk, 1e-12f));
+        }
+        const float4 G4 = *reinterpret_cast<const float4*>(Gsm + tok * D + 4 * lane);
+        const float Gv[4] = {G4.x, G4.y, G4.z, G4.w};
+        float kds[4], qds[4], kis[4], kdt[4], qdt[4], krr[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const float e = fminf(fmaxf(Gv[j] - rr[j], -126.0f), 126.0f);
+          const float E = ex2f(e), Ei = ex2f(-e);
+          const float kn = kf[j] * kinv, qn = qf[j] * qinv;
+          kds[j] = kn * E; qds[j] = qn * E; kis[j] = kn * Ei;
+          kdt[j] = kds[j] * er[j]; qdt[j] = qds[j] * er[j]; krr[j] = kis[j] * elr[j];
+        }
+        // in place: the decayed bf16 tiles of the intra-chunk products replace the raw q / k tiles
+        *reinterpret_cast<uint2*>(raw + RAW_K + off) = make_uint2(pack_bf16(kds[0], kds[1]), pack_bf16(kds[2], kds[3]));
+        *reinterpret_cast<uint2*>(raw + RAW_Q + off) = make_uint2(pack_bf16(qds[0], qds[1]), pack_bf16(qds[2], qds[3]));
+        *reinterpret_cast<uint2*>(x.smem + OFF_KIS + off) = make_uint2(pack_bf16(kis[0], kis[1]), pack_bf16(kis[2], kis[3]));
+        // tf32 operands of the state products: [kd ; qd] K-major (row = token / 32 + token), kr MN-major
+        *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(tok, 4 * lane, 8192)) = make_float4(kdt[0], kdt[1], kdt[2], kdt[3]);
+        *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(32 + tok, 4 * lane, 8192)) = make_float4(qdt[0], qdt[1], qdt[2], qdt[3]);
+        *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, tok, 512, 2048)) = make_float4(krr[0], krr[1], krr[2], krr[3]);
+      }
+    }
+    PROF_STAMP(2, 27);
+    prep_bar();
+    PROF_STAMP(2, 28);
+
+    // ---- C: one 16x16 block of A = kd' ki'^T (warps 0-3) or M = qd' ki'^T (warps 4-7) per warp
+    {
+      const int which = pw >> 2, rb = (pw >> 1) & 1, cb = pw & 1;
+      const float* beta_s = reinterpret_cast<const float*>(x.smem + OFF_BETA) + s * 32;
+      float acc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+      if (!(rb == 0 && cb == 1)) {
+        const uint32_t a_tile = smem_u32(raw + (which ? RAW_Q : RAW_K));
+        const uint32_t b_tile = smem_u32(x.smem + OFF_KIS);
+        const int a_row = 16 * rb + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int b_row = 16 * cb + 8 * (lane >> 4) + (lane & 7);
+#pragma unroll
+        for (int kt = 0; kt < 8; kt++) {
+          uint32_t a[4], b[4];
+          ldmatrix_x4(a, a_tile + tile128_off(a_row, (2 * kt + (lane >> 4)) * 8));
+          ldmatrix_x4(b, b_tile + tile128_off(b_row, (2 * kt + ((lane >> 3) & 1)) * 8));
+          mma_bf16(acc[0], a, b[0], b[1]);
+          mma_bf16(acc[1], a, b[2], b[3]);
+        }
+      }
+      const int g = lane >> 2, t = lane & 3;
+      const int i0 = 16 * rb + g, i1 = i0 + 8;
+      if (which == 0) {
+        x.wait(B_L_EMPTY + s, par ^ 1, E_PREP);
+        float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
+        const float b0 = beta_s[i0], b1 = beta_s[i1];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const int j = 16 * cb + 8 * nt + 2 * t;
+          *reinterpret_cast<float2*>(Lsm + i0 * C + j) = make_float2((j < i0) ? acc[nt][0] * b0 : 0.0f, (j + 1 < i0) ? acc[nt][1] * b0 : 0.0f);
+          *reinterpret_cast<float2*>(Lsm + i1 * C + j) = make_float2((j < i1) ? acc[nt][2] * b1 : 0.0f, (j + 1 < i1) ? acc[nt][3] * b1 : 0.0f);
+        }
+        if (pw == 0) reinterpret_cast<float*>(x.smem + OFF_LBETA)[s * 32 + lane] = beta_s[lane];
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const int j = 16 * cb + 8 * nt + 2 * t;
+          *reinterpret_cast<float2*>(cons + CS_M + kmajor_f32_off(i0, j, 0)) =
+              make_float2((j <= i0) ? acc[nt][0] : 0.0f, (j + 1 <= i0) ? acc[nt][1] : 0.0f);
+          *reinterpret_cast<float2*>(cons + CS_M + kmajor_f32_off(i1, j, 0)) =
+              make_float2((j <= i1) ? acc[nt][2] : 0.0f, (j + 1 <= i1) ? acc[nt][3] : 0.0f);
+        }
+      }
+    }
+    PROF_STAMP(2, 29);
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(x.bar(B_P1_FULL + s));
+      mbar_arrive(x.bar(B_L_FULL + s));
+      mbar_arrive(x.bar(B_RAW_EMPTY + s));
+    }
+  }
+  (void)v_zero;
+}
+
+// ------------------------------------------------------------------------------------------------ inverse warps
+__device__ void role_inverse(const Ctx& x, int which, int lane) {
+  for (int c = which; c < x.nchunks; c += 2) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    x.wait(B_L_FULL + s, par, E_INV);
+    const float* Lsm = reinterpret_cast<const float*>(x.smem + OFF_L) + s * 1024;
+    PROF_BEGIN;
+    float Tc[C];
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll
+      for (int j = 0; j + 3 < i; j += 4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(Lsm + i * C + j);
+        a0 = fmaf(l4.x, Tc[j], a0);
+        a1 = fmaf(l4.y, Tc[j + 1], a1);
+        a2 = fmaf(l4.z, Tc[j + 2], a2);
+        a3 = fmaf(l4.w, Tc[j + 3], a3);
+      }
+#pragma unroll
+      for (int j = i & ~3; j < i; j++) a0 = fmaf(Lsm[i * C + j], Tc[j], a0);
+      Tc[i] = ((i == lane) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
+    }
+    const float bc = reinterpret_cast<const float*>(x.smem + OFF_LBETA)[s * 32 + lane];
+    PROF_STAMP(3, 26);
+    x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
+    uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
+    uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      const float val = Tc[i] * bc;
+      *reinterpret_cast<float*>(tb + kmajor_f32_off(i, lane, 0)) = val;
+      *reinterpret_cast<__nv_bfloat16*>(tbh + kmajor_b16_sw64_off(i, lane)) = __float2bfloat16_rn(val);
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(x.bar(B_INV_FULL + s));
+      mbar_arrive(x.bar(B_L_EMPTY + s));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ MMA issuer
+__device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
+  const uint32_t sb = smem_u32(x.smem);
+  constexpr uint32_t ID1 = make_idesc(FMT_TF32, 128, 64, 0, 0, 0);
+  constexpr uint32_t ID2A = make_idesc(FMT_BF16, 128, 32, 1, 0, 0);
+  constexpr uint32_t ID2B = make_idesc(FMT_TF32, 128, 32, 0, 0, 1);
+  constexpr uint32_t ID3A = make_idesc(FMT_TF32, 128, 128, 0, 1, 0);
+  constexpr uint32_t ID3B = make_idesc(FMT_TF32, 128, 32, 0, 0, 0);
+  const uint32_t tS = tmem + TM_S, tU = tmem + TM_U;
+  x.wait1(B_S_READY, 0, E_MMA);                    // initial state is in tensor memory
+  for (int c = 0; c < x.nchunks; c++) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    const uint32_t cons = sb + OFF_CONS + s * CS_STAGE;
+    const uint32_t tWO = tmem + TM_WO + 64 * s;
+    x.wait1(B_P1_FULL + s, par, E_MMA);
+    x.wait1(B_O_EMPTY + s, par ^ 1, E_MMA);
+    tc_fence_after();
+#pragma unroll
+    for (int ks = 0; ks < 16; ks++)
+      mma_ts_tf32(tWO, tS + 8 * ks, make_sdesc(cons + CS_KDQD + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, LAYOUT_SW128), ID1, ks > 0);
+    mma_commit(x.bar(B_MMA1_DONE));
+    x.wait1(B_INV_FULL + s, par, E_MMA);
+    tc_fence_after();
+    if (!v_zero) {
+#pragma unroll
+      for (int ks = 0; ks < 2; ks++)
+        mma_ss_f16(tU, make_sdesc(cons + CS_V + 2 * ks * 1024, 4096, 1024, LAYOUT_SW128),
+                   make_sdesc(sb + OFF_TBH + s * 2048 + ks * 32, 16, 512, LAYOUT_SW64), ID2A, ks > 0);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32(tU, tWO + 8 * ks, make_sdesc(cons + CS_TB + ks * 32, 16, 1024, LAYOUT_SW128), ID2B, (ks > 0) || !v_zero);
+    x.wait1(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA);   // scaler finished St <- St diag(2^G31)
+    tc_fence_after();
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32(tS, tU + 8 * ks, make_sdesc(cons + CS_KR + ks * 4096, 512, 2048, LAYOUT_SW128_BASE32B), ID3A, 1);
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32(tWO + 32, tU + 8 * ks, make_sdesc(cons + CS_M + ks * 32, 16, 1024, LAYOUT_SW128), ID3B, 1);
+    mma_commit(x.bar(B_O_FULL + s));
+    mma_commit(x.bar(B_CONS_EMPTY + s));
+  }
+  mma_commit(x.bar(B_MMA1_DONE));                  // the final state is complete
+  mma_commit(x.bar(B_DRAIN));
+  x.wait1(B_DRAIN, 0, E_MMA);
+}
+
+// ------------------------------------------------------------------------------------------------ scaler warps
+template <typename OutT>
+__device__ __forceinline__ void store_row_piece(OutT* dst_head, int key_first, int v, int col0, const uint32_t (&r)[32]);
+
+template <>
+__device__ __forceinline__ void store_row_piece<float>(float* dst, int key_first, int v, int col0, const uint32_t (&r)[32]) {
+  if (!key_first) {
+    float4* d = reinterpret_cast<float4*>(dst + v * D + col0);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      d[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i++) dst[(col0 + i) * D + v] = __uint_as_float(r[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_row_piece<__nv_bfloat16>(__nv_bfloat16* dst, int key_first, int v, int col0, const uint32_t (&r)[32]) {
+  if (!key_first) {
+    uint4* d = reinterpret_cast<uint4*>(dst + v * D + col0);
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      d[i] = make_uint4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])), pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                        pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])), pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i++) dst[(col0 + i) * D + v] = __float2bfloat16_rn(__uint_as_float(r[i]));
+  }
+}
+
+__device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
+  const int v = 32 * quarter + lane;
+  const uint32_t tS = tmem + TM_S + ((uint32_t)(32 * quarter) << 16);
+  // ---- initial state -> tensor memory
+#pragma unroll 1
+  for (int j = 0; j < 4; j++) {
+    uint32_t r[32];
+    if (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY)) {
+      const float one = (task.flags & TF_INIT_IDENTITY) ? 1.0f : 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; i++) r[i] = __float_as_uint((32 * j + i == v) ? one : 0.0f);
+    } else {
+      const float* src = task.src + (size_t)x.h * STATE_ELEMS;
+      if (!p.key_first) {
+        const float4* s4 = reinterpret_cast<const float4*>(src + v * D + 32 * j);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float4 f = s4[i];
+          r[4 * i] = __float_as_uint(f.x); r[4 * i + 1] = __float_as_uint(f.y); r[4 * i + 2] = __float_as_uint(f.z); r[4 * i + 3] = __float_as_uint(f.w);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(src[(32 * j + i) * D + v]);
+      }
+    }
+    tmem_st32(tS + 32 * j, r);
+  }
+  tmem_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(x.bar(B_S_READY));
+
+  for (int c = 0; c <= x.nchunks; c++) {
+    x.wait(B_MMA1_DONE, (uint32_t)(c & 1), E_SCALE);
+    tc_fence_after();
+    const bool last = c == x.nchunks;
+    const bool ck = !last && task.ck != nullptr && p.ck_every_chunks > 0 && (c % p.ck_every_chunks) == 0;
+    const float* dec = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 1) * D;
+    long long ck_off = 0;
+    if (ck) ck_off = (long long)(c / p.ck_every_chunks) * p.ck_row_stride + (long long)x.h * STATE_ELEMS;
+#pragma unroll 1
+    for (int j = 0; j < 4; j++) {
+      uint32_t r[32];
+      tmem_ld32(tS + 32 * j, r);
+      tmem_wait_ld();
+      if (ck) {
+        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, p.key_first, v, 32 * j, r);
+        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, p.key_first, v, 32 * j, r);
+      }
+      if (last) {
+        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, p.key_first, v, 32 * j, r);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float4 d4 = *reinterpret_cast<const float4*>(dec + 32 * j + 4 * i);
+          r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) * d4.x);
+          r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * d4.y);
+          r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * d4.z);
+          r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * d4.w);
+        }
+        tmem_st32(tS + 32 * j, r);
+      }
+    }
+    if (!last) {
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x.bar(B_S_READY));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ epilogue warps
+__device__ void role_epilogue(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
+  const int v = 32 * quarter + lane;
+  __nv_bfloat16* obase = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
+  for (int c = 0; c < x.nchunks; c++) {
+    const int s = c & 1;
+    x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI);
+    tc_fence_after();
+    uint32_t r[32];
+    tmem_ld32(tmem + TM_WO + 64 * s + 32 + ((uint32_t)(32 * quarter) << 16), r);
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + s));
+    if (!(task.flags & TF_NO_OUT)) {
+      const int nvalid = min(C, x.len - c * C);
+      __nv_bfloat16* o = obase + (x.t0 + (long long)c * C) * p.ldo;
+#pragma unroll
+      for (int i = 0; i < C; i++)
+        if (i < nvalid) o[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(r[i]));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.H;
+  const int rank = blockIdx.x / H, h = blockIdx.x % H;
+
+  if (p.status[0] & 1) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
+    const long long rows = p.T * H;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x)
+      if (tid < 16) reinterpret_cast<uint4*>(p.out + (r / H) * p.ldo + (r % H) * D)[tid] = make_uint4(0, 0, 0, 0);
+  }
+  if (rank >= *p.n_tasks) return;
+  const Task task = p.tasks[rank];
+  Ctx x;
+  x.smem = smem;
+  x.bars = smem_u32(smem + OFF_BAR);
+  x.abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
+  x.h = h;
+  x.len = task.len;
+  x.nchunks = (task.len + C - 1) / C;
+  x.t0 = task.t0;
+#ifdef KDA_PROF
+  x.prof = reinterpret_cast<unsigned long long*>(p.status + 16);
+  const long long prof_t0 = clock64();
+#endif
+
+  if (x.nchunks == 0) {
+    // empty run: the state passes through (source -> destination) without touching tensor memory
+    if (task.dst != nullptr) {
+      float* dst = task.dst + (size_t)h * STATE_ELEMS;
+      const float* src = (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY)) ? nullptr : task.src + (size_t)h * STATE_ELEMS;
+      if (src != dst) {
+        for (int i = tid; i < STATE_ELEMS / 4; i += THREADS) {
+          float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (src != nullptr) f = reinterpret_cast<const float4*>(src)[i];
+          else if (task.flags & TF_INIT_IDENTITY) {
+            const int row = (4 * i) / D, col = (4 * i) % D;
+            f = make_float4(row == col ? 1.f : 0.f, row == col + 1 ? 1.f : 0.f, row == col + 2 ? 1.f : 0.f, row == col + 3 ? 1.f : 0.f);
+          }
+          reinterpret_cast<float4*>(dst)[i] = f;
+        }
+      }
+    }
+    return;
+  }
+
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+  if (tid == 0) {
+    *x.abort_flag = 0;
+    for (int i = 0; i < 2; i++) {
+      mbar_init(x.bar(B_RAW_FULL + i), 1);
+      mbar_init(x.bar(B_RAW_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_CONS_EMPTY + i), 1);
+      mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
+      mbar_init(x.bar(B_INV_FULL + i), 1);
+      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS);
+      mbar_init(x.bar(B_L_EMPTY + i), 1);
+      mbar_init(x.bar(B_O_FULL + i), 1);
+      mbar_init(x.bar(B_O_EMPTY + i), 4);
+    }
+    mbar_init(x.bar(B_MMA1_DONE), 1);
+    mbar_init(x.bar(B_S_READY), 4);
+    mbar_init(x.bar(B_DRAIN), 1);
+    fence_barrier_init();
+  }
+  if (warp == W_MMA) {
+    tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const bool v_zero = (task.flags & TF_V_ZERO) != 0;
+
+  if (warp == W_MMA) {
+    if (lane == 0) role_mma(x, tmem, v_zero);
+    __syncwarp();
+  } else if (warp == W_INV0 || warp == W_INV0 + 1) {
+    role_inverse(x, warp - W_INV0, lane);
+  } else if (warp == W_LOAD) {
+    role_loader(p, x, lane, v_zero);
+  } else if (warp < W_EPI0) {
+    role_scaler(p, task, x, tmem, warp & 3, lane);
+  } else if (warp < W_PREP0) {
+    role_epilogue(p, task, x, tmem, warp & 3, lane);
+  } else {
+    role_prep(p, x, tid - W_PREP0 * 32, v_zero);
+  }
+
+#ifdef KDA_PROF
+  if (lane == 0 && blockIdx.x == 0) {
+    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_EPI0 ? 5 : (warp < W_PREP0 ? 6 : 2))));
+    atomicAdd(x.prof + role * 32 + 24, (unsigned long long)(clock64() - prof_t0));
+    atomicAdd(x.prof + role * 32 + 25, 1ull);
+  }
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *x.abort_flag != 0) atomicCAS(p.status + 2, 0, *x.abort_flag);
+  if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
+}
+
+}  // namespace u
+
+cudaError_t launch_chunk_umma(const ChunkParams& p, int n_task_cap, cudaStream_t stream) {
+  static int attr_dev_mask = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_dev_mask & (1 << (dev & 31)))) {
+    cudaError_t e = cudaFuncSetAttribute(u::kda_chunk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, u::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_dev_mask |= 1 << (dev & 31);
+  }
+  const long long blocks = (long long)n_task_cap * p.H;
+  if (blocks <= 0) return cudaSuccess;
+  u::kda_chunk_umma_kernel<<<(unsigned)blocks, u::THREADS, u::SMEM_BYTES, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace kda

@@ -24,6 +24,7 @@ struct PlanParams {
 };
 
 cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream);
-cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);
+cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);    // mma.sync kernel
+cudaError_t launch_chunk_umma(const ChunkParams& p, int n_task_cap, cudaStream_t stream);   // tcgen05 kernel
 
 }  // namespace kda

@@ -22,6 +22,7 @@ owns output / workspace tensors and passes raw device pointers.  There is no CPU
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -32,6 +33,12 @@ CHUNK = 32
 LOWER_BOUND = -5.0   # the reference fixes the gate's lower bound (kda/b200/csrc/w3/base/kernel.py:723)
 
 __all__ = ["kda_prefill", "run", "prepare", "status_bits", "chunk_kda", "prepare_plain"]
+
+
+def default_kernel():
+    """Kernel used by new launches: the tcgen05 kernel, unless KDA_B200_KERNEL=mma_sync selects the warp-level
+    cross-check kernel (read when a launch is prepared, not on the hot path)."""
+    return _cabi.KERNEL_MMA_SYNC if os.environ.get("KDA_B200_KERNEL", "") == "mma_sync" else _cabi.KERNEL_TCGEN05
 
 
 def _err(msg):
@@ -161,7 +168,7 @@ def kernel_error(launch):
 
 def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens, *, raw, key_first,
              ssm_state_indices=None, state_checkpoints=None, checkpoint_cu_starts=None, checkpoint_every_n_tokens=0,
-             initial_state_source=None, initial_state_indices=None, dynamic_layout=False, want_final=True):
+             initial_state_source=None, initial_state_indices=None, dynamic_layout=False, want_final=True, kernel=None):
     cu_seqlens = _check_args(q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens, dynamic_layout, raw)
     dev = q.device
     T, H = q.shape[1], q.shape[2]
@@ -293,6 +300,7 @@ def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens,
         a.ck_starts, a.ck_starts_is64 = ck_starts.data_ptr(), int(ck_starts.dtype == torch.int64)
     a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
     a.status = status.data_ptr()
+    a.kernel = default_kernel() if kernel is None else int(kernel)
 
     keep += [q_, k_, v_, g_, beta_, A_, dtb_, cu_seqlens, src, dst, d_idx, s_idx, ck, ck_starts, workspace, status, out]
     result = (out, dst) if not every else (out, dst, state_checkpoints)

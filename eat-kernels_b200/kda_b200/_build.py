@@ -9,7 +9,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG.parent / "csrc"
 LIB = PKG / "libkda_b200.so"
-SOURCES = ["kda_chunk_fwd.cu", "kda_plan.cu", "kda_cp.cu", "kda_capi.cu"]
+SOURCES = ["kda_chunk_umma.cu", "kda_chunk_fwd.cu", "kda_plan.cu", "kda_cp.cu", "kda_capi.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-shared"]
 

@@ -10,6 +10,7 @@ LIB_PATH = PKG / "libkda_b200.so"
 
 FRONTEND_RAW, FRONTEND_PLAIN = 0, 1
 STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
+KERNEL_TCGEN05, KERNEL_MMA_SYNC = 0, 1
 EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_segment_launch", "kda_scan_launch",
            "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version"]
 
@@ -33,6 +34,7 @@ class KdaPrefillArgs(C.Structure):
         ("ck_starts", C.c_void_p), ("ck_starts_is64", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+        ("kernel", C.c_int32),
     ]
 
 

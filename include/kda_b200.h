@@ -48,6 +48,13 @@ enum {
   KDA_STATE_KEY_FIRST = 1      /* [.., 128 (K), 128 (V)] */
 };
 
+/* Which fused chunk kernel runs the recurrence. */
+enum {
+  KDA_KERNEL_TCGEN05 = 0,  /* tcgen05 / tensor-memory kernel (default) */
+  KDA_KERNEL_MMA_SYNC = 1  /* warp-level mma.sync kernel: same results within tolerance, kept as an independent
+                              cross-check of the tensor-memory path */
+};
+
 /* Bits of status[0] (table validation, same meaning as kda/b200/kda_b200.py:56-62). */
 enum {
   KDA_STATUS_BAD_CU = 1,        /* cu_seqlens rejected: every sequence treated as empty, output rows zero-filled */
@@ -105,7 +112,9 @@ typedef struct KdaPrefillArgs {
                              survive between calls, but concurrent calls must not share it */
   size_t workspace_bytes;
   int32_t* status;        /* device int32[4]: [0] table-validation bits, [1] reserved, [2] kernel error code
-                             (0 = none), [3] reserved; written by every call */
+                             (0 = none; nonzero: a bounded wait inside the kernel gave up, results are invalid),
+                             [3] reserved; written by every call */
+  int32_t kernel;         /* KDA_KERNEL_* */
 } KdaPrefillArgs;
 
 /* Bytes of workspace a call with N sequences and H heads needs. */
