@@ -1,0 +1,177 @@
+"""Multi-GPU execution of KDA prefill: head parallelism and context parallelism (one process per GPU).
+
+Head parallelism needs no communication: heads are independent, so rank r runs the ordinary call on its head slice
+(`head_slice`), reading strided views of wider tensors in place.
+
+Context parallelism splits ONE long sequence over tokens.  The recurrence is affine in the state, so a token segment
+that does not know its entering state yet can still be processed (value-first orientation, as
+kda/b200/csrc/w3/kernel.py:22-38 and kda/b200/csrc/w3/cp_fix.cu:4-21 of the reference do inside one GPU):
+
+    chain L  (S0 = 0, real v)   ->  o_loc, S_loc            chain Tr (S0 = I, v = 0)   ->  Qt, P
+    S_end = S_in @ P + S_loc            out_t = o_loc_t + S_in applied to Qt_t
+
+Every rank cuts its token shard into `pieces` chunk-aligned pieces (more pieces = more CTAs to fill 148 SMs), runs both
+chains per piece in one launch, composes its pieces into one map per head, all-gathers the per-rank maps
+(2 x H x 64 KB fp32 per rank) over NCCL, scans them to get its entering state, scans its own pieces from there and
+fixes the outputs up.  The first piece of rank 0 knows its entering state (the caller's initial state), runs the plain
+chain and contributes the map (P = 0, S_loc = its true end state), which keeps the algebra uniform.
+
+The three compute steps go through the C ABI (kda_segment_launch, kda_scan_launch, kda_fixup_launch).  They are
+grouped in a backend object so that the orchestration (piece boundaries, gather layout, scan order) can be exercised
+on CPU ranks with a stand-in backend supplied by the tests; the package itself ships only the CUDA backend.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _cabi
+
+D = 128
+CHUNK = 32
+
+
+def head_slice(rank, world, *tensors, heads_dim=2):
+    """Views of the heads owned by `rank` (contiguous block of H/world heads) of [1,T,H,...] token tensors."""
+    out = []
+    for t in tensors:
+        H = t.shape[heads_dim]
+        if H % world:
+            raise ValueError(f"KDA kernel: {H} heads do not shard evenly over {world} ranks")
+        hs = H // world
+        out.append(t.narrow(heads_dim, rank * hs, hs))
+    return out
+
+
+def split_pieces(T, pieces):
+    """Chunk-aligned piece boundaries of a shard of T tokens: `pieces` near-equal runs (fewer when T is short)."""
+    nchunks = -(-T // CHUNK)
+    pieces = max(1, min(pieces, nchunks))
+    base, extra = divmod(nchunks, pieces)
+    bounds, c = [0], 0
+    for i in range(pieces):
+        c += base + (1 if i < extra else 0)
+        bounds.append(min(T, c * CHUNK))
+    return bounds
+
+
+class CudaBackend:
+    """The shipped backend: the three context-parallel steps on the current CUDA device through the C ABI."""
+
+    def __init__(self, kernel=None):
+        from . import default_kernel
+        self.lib = _cabi.lib()
+        self.kernel = default_kernel() if kernel is None else int(kernel)
+
+    @staticmethod
+    def _stream(dev):
+        return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def segment_maps(self, q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first_state):
+        """Runs chain L (and chain Tr where need_map) for the pieces [bounds[i], bounds[i+1]).
+        Returns out [1,T,H,128] bf16 (o_loc), qt [1,T,H,128] bf16, P, S_loc [n,H,128,128] fp32 (value-first)."""
+        dev = q.device
+        T, H = q.shape[1], q.shape[2]
+        n = len(bounds) - 1
+        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device=dev)
+        qt = torch.empty(1, T, H, D, dtype=torch.bfloat16, device=dev)
+        P = torch.zeros(n, H, D, D, dtype=torch.float32, device=dev)
+        S_loc = torch.empty(n, H, D, D, dtype=torch.float32, device=dev)
+        t0 = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
+        t1 = torch.tensor(bounds[1:], dtype=torch.int64, device=dev)
+        nm = torch.tensor(need_map, dtype=torch.int32, device=dev)
+        ws_bytes = self.lib.kda_prefill_workspace_bytes(2 * n, H)
+        ws = torch.zeros(ws_bytes + 256, dtype=torch.uint8, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        s = _cabi.KdaSegmentArgs()
+        a = s.base
+        a.q, a.k, a.v, a.g, a.beta, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), out.data_ptr()
+        a.ldq, a.ldk, a.ldv, a.ldg = (t.stride(1) if T > 1 else H * D for t in (q, k, v, g))
+        a.ldbeta = beta.stride(1) if T > 1 else H
+        a.ldo = H * D
+        a.A_log = A_log.data_ptr() if raw else None
+        a.dt_bias = dt_bias.data_ptr() if raw else None
+        a.scale, a.lower_bound = float(scale), -5.0
+        a.frontend = _cabi.FRONTEND_RAW if raw else _cabi.FRONTEND_PLAIN
+        a.state_layout = _cabi.STATE_VALUE_FIRST
+        a.H, a.N, a.T = H, n, T
+        if first_state is not None:
+            a.src_base, a.src_slot_stride, a.src_slots = first_state.data_ptr(), first_state.stride(0), first_state.shape[0]
+        a.workspace, a.workspace_bytes = (ws.data_ptr() + 255) // 256 * 256, ws_bytes
+        a.status = status.data_ptr()
+        a.kernel = self.kernel
+        s.n_seg = n
+        s.seg_t0, s.seg_t1, s.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
+        s.qt, s.P, s.S_loc = qt.data_ptr(), P.data_ptr(), S_loc.data_ptr()
+        _cabi.check(self.lib.kda_segment_launch(C.byref(s), self._stream(dev)), "kda_segment_launch")
+        self._keep = (t0, t1, nm, ws, status)       # alive until the stream has consumed them
+        return out, qt, P, S_loc
+
+    def scan(self, P, S_loc, S0):
+        """S_in[0] = S0 (or 0), S_in[i+1] = S_in[i] @ P[i] + S_loc[i]; returns (S_in [n,H,128,128], S_end [H,128,128])."""
+        n, H = P.shape[0], P.shape[1]
+        S_in = torch.empty_like(S_loc)
+        S_end = torch.empty(H, D, D, dtype=torch.float32, device=P.device)
+        _cabi.check(self.lib.kda_scan_launch(P.data_ptr(), S_loc.data_ptr(), None if S0 is None else S0.data_ptr(),
+                                             S_in.data_ptr(), S_end.data_ptr(), n, H, self._stream(P.device)), "kda_scan_launch")
+        return S_in, S_end
+
+    def fixup(self, out, qt, S_in, bounds, need_map):
+        dev = out.device
+        n, H = len(bounds) - 1, out.shape[2]
+        t0 = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
+        t1 = torch.tensor(bounds[1:], dtype=torch.int64, device=dev)
+        nm = torch.tensor(need_map, dtype=torch.int32, device=dev)
+        _cabi.check(self.lib.kda_fixup_launch(out.data_ptr(), qt.data_ptr(), H * D, S_in.data_ptr(), t0.data_ptr(), t1.data_ptr(),
+                                              nm.data_ptr(), n, H, self._stream(dev)), "kda_fixup_launch")
+        self._keep2 = (t0, t1, nm)
+        return out
+
+
+def compose_rank_map(backend, P, S_loc):
+    """Total map of a rank's pieces per head: P_rank = P_0 @ P_1 @ ..., L_rank = (..(S_loc_0 @ P_1 + S_loc_1) @ P_2 ..)."""
+    n = P.shape[0]
+    _, L_rank = backend.scan(P, S_loc, None)
+    if n == 1:
+        return P[0].clone(), L_rank
+    _, P_rank = backend.scan(P[1:], torch.zeros_like(S_loc[1:]), P[0].contiguous())
+    return P_rank, L_rank
+
+
+def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_state=None, *, group=None, pieces=2,
+                             raw=True, backend=None):
+    """Context-parallel prefill of ONE sequence whose tokens are sharded over the ranks of `group` in rank order.
+
+    q, k, v, g [1, T_local, H, 128] and beta [1, T_local, H] are this rank's shard (contiguous token rows);
+    initial_state [1, H, 128, 128] fp32 value-first is read on rank 0 (zeros when None).  With `group=None` (or a
+    single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.
+    Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank)."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    backend = backend or CudaBackend()
+    T, H = q.shape[1], q.shape[2]
+    bounds = split_pieces(T, pieces)
+    n = len(bounds) - 1
+    need_map = [1] * n
+    first = None
+    if rank == 0:
+        need_map[0] = 0            # the first piece of the sequence starts from the caller's state: plain chain
+        first = initial_state if initial_state is not None else torch.zeros(1, H, D, D, dtype=torch.float32, device=q.device)
+    out, qt, P, S_loc = backend.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first)
+    # P of an unmapped piece is the zero map (its S_loc is the true end state): segment_maps leaves it zero-filled
+    P_rank, L_rank = compose_rank_map(backend, P, S_loc)
+    if world > 1:
+        mine = torch.stack([P_rank, L_rank])                               # [2, H, 128, 128]
+        gathered = torch.empty(world, *mine.shape, dtype=mine.dtype, device=mine.device)
+        dist.all_gather_into_tensor(gathered.view(world * 2, *mine.shape[1:]), mine, group=group)
+        S_in_ranks, S_final = backend.scan(gathered[:, 0].contiguous(), gathered[:, 1].contiguous(), None)
+        S_enter = S_in_ranks[rank]
+    else:
+        S_enter = None
+        S_final = L_rank
+    S_in, _ = backend.scan(P, S_loc, S_enter)
+    out = backend.fixup(out, qt, S_in, bounds, need_map)
+    return out, S_final[None]

@@ -1,0 +1,74 @@
+"""GPU parity of the context-parallel path (segment maps, scan, fix-up) and the state row copies, through the C ABI.
+Single GPU: the pieces are segments of one chain, the same algebra that runs across ranks (the multi-rank
+orchestration is covered on CPU ranks by tests/test_parallel_cpu.py)."""
+import ctypes as C
+
+import pytest
+import torch
+
+import kda_oracle as ko
+from kda_testlib import DEV, D, gold_raw, slow_gates_, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def kda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import kda_b200
+    return kda_b200
+
+
+@pytest.mark.parametrize("H,T,pieces,slow,kernel", [(4, 1000, 4, False, 0), (2, 2048, 3, True, 0), (8, 333, 8, False, 0),
+                                                    (4, 1000, 4, False, 1), (3, 97, 2, False, 0), (2, 40, 5, False, 0)])
+def test_context_parallel_single_gpu(kda, H, T, pieces, slow, kernel):
+    from kda_b200 import parallel
+    inputs = ko.make_inputs_raw(H, [T], 40 + H + pieces)
+    if slow:
+        slow_gates_(inputs, 40)
+    gold_o, gold_s, _ = gold_raw(inputs, [T])
+    q, k, v, g, beta, A_log, dt_bias, scale, init, _ = to_dev(inputs)
+    out, fin = parallel.context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, init, pieces=pieces,
+                                                 backend=parallel.CudaBackend(kernel=kernel))
+    torch.cuda.synchronize()
+    tag = f"cp H={H} T={T} pieces={pieces} slow={slow} kernel={kernel}"
+    ko.check_close(out.cpu(), gold_o, tag + " output")
+    ko.check_close(fin.cpu(), gold_s, tag + " final_state")
+    # and against the ordinary single-chain call on the same device
+    o2, f2 = kda.run(q, k, v, g, beta, A_log, dt_bias, scale, init)
+    ko.check_close(out.cpu(), o2.cpu(), tag + " vs plain call (output)", 6e-3)
+    ko.check_close(fin.cpu(), f2.cpu(), tag + " vs plain call (state)", 6e-3)
+
+
+def test_scan_matches_fp64(kda):
+    from kda_b200 import parallel
+    be = parallel.CudaBackend()
+    gen = torch.Generator().manual_seed(5)
+    n, H = 5, 3
+    P = (torch.randn(n, H, D, D, generator=gen) * 0.08)
+    L = torch.randn(n, H, D, D, generator=gen)
+    S0 = torch.randn(H, D, D, generator=gen)
+    S_in, S_end = be.scan(P.to(DEV), L.to(DEV), S0.to(DEV))
+    cur = S0.double()
+    for i in range(n):
+        assert torch.allclose(S_in[i].cpu().double(), cur, rtol=1e-4, atol=1e-4)
+        cur = cur @ P[i].double() + L[i].double()
+    assert torch.allclose(S_end.cpu().double(), cur, rtol=1e-4, atol=1e-4)
+
+
+def test_state_rows_copy(kda):
+    from kda_b200 import _cabi
+    lib = _cabi.lib()
+    H = 3
+    src = torch.randn(6, H, D, D, device=DEV)
+    idx = torch.tensor([4, 0, 5], dtype=torch.int32, device=DEV)
+    dst = torch.zeros(3, H, D, D, device=DEV)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.kda_state_rows_copy(dst.data_ptr(), H * D * D, 0, src.data_ptr(), H * D * D, idx.data_ptr(), 3, H, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src[idx.long()])
+    dstb = torch.zeros(3, H, D, D, device=DEV, dtype=torch.bfloat16)
+    assert lib.kda_state_rows_copy(dstb.data_ptr(), H * D * D, 1, src.data_ptr(), H * D * D, idx.data_ptr(), 3, H, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dstb, src[idx.long()].to(torch.bfloat16))       # round to nearest even
