@@ -137,6 +137,42 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   return KDA_OK;
 }
 
+}  // extern "C"
+
+// ---- scratch of kda_prefill_launch_noalloc: a fixed device array instead of a caller workspace.  In host code the
+// name below is only a handle of the symbol, not a device address; the address is looked up per device with
+// cudaGetSymbolAddress and cached.
+namespace {
+constexpr size_t kNoallocBytes = 2 * 12288 /* task tables, 64 x 48 B each rounded up */ + 256 /* task count */ +
+                                 1024 /* cu_seqlens copy */ + (size_t)KDA_NOALLOC_MAX_HEADS * kda::STATE_ELEMS * sizeof(float) + 4096;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocBytes];
+constexpr int kMaxDevices = 64;
+void* g_noalloc_addr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" {
+
+int kda_prefill_launch_noalloc(const KdaPrefillArgs* a, void* stream_) {
+  if (a == nullptr) return KDA_ERR_ARG;
+  if (a->N > KDA_NOALLOC_MAX_SEQS || a->H > KDA_NOALLOC_MAX_HEADS) return KDA_ERR_LIMIT;
+  if (a->N < 1 || a->H < 1) return KDA_ERR_ARG;
+  if (carve(nullptr, a->N, a->H).bytes > kNoallocBytes) return KDA_ERR_LIMIT;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= kMaxDevices) return KDA_ERR_LIMIT;
+  if (g_noalloc_addr[dev] == nullptr) {       // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e);
+    g_noalloc_addr[dev] = ptr;
+  }
+  KdaPrefillArgs b = *a;
+  b.workspace = g_noalloc_addr[dev];
+  b.workspace_bytes = kNoallocBytes;
+  return kda_prefill_launch(&b, stream_);
+}
+
 int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (s == nullptr) return KDA_ERR_ARG;

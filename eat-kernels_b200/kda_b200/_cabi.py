@@ -10,8 +10,9 @@ LIB_PATH = PKG / "libkda_b200.so"
 
 FRONTEND_RAW, FRONTEND_PLAIN = 0, 1
 STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
+NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
 KERNEL_TCGEN05, KERNEL_MMA_SYNC = 0, 1
-EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_segment_launch", "kda_scan_launch",
+EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
            "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version"]
 
 
@@ -62,6 +63,8 @@ def lib():
         L.kda_prefill_workspace_bytes.restype = C.c_size_t
         L.kda_prefill_launch.argtypes = [C.POINTER(KdaPrefillArgs), C.c_void_p]
         L.kda_prefill_launch.restype = C.c_int
+        L.kda_prefill_launch_noalloc.argtypes = [C.POINTER(KdaPrefillArgs), C.c_void_p]
+        L.kda_prefill_launch_noalloc.restype = C.c_int
         L.kda_segment_launch.argtypes = [C.POINTER(KdaSegmentArgs), C.c_void_p]
         L.kda_segment_launch.restype = C.c_int
         L.kda_scan_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

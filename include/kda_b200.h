@@ -124,6 +124,24 @@ size_t kda_prefill_workspace_bytes(int32_t N, int32_t H);
  * chunk kernel.  Two kernel launches, no host read of any table. */
 int kda_prefill_launch(const KdaPrefillArgs* args, void* stream);
 
+/* The same call for callers that must not allocate device memory and have no workspace to hand over: code running
+ * inside a memory-pool callback or an allocator hook, a process whose device memory is fully reserved up front by a
+ * serving engine, or a thread that may be inside CUDA stream capture (where cudaMalloc is illegal).  The scratch lives
+ * in a fixed array inside the library's device image instead of `args->workspace` (which is ignored, as is
+ * `workspace_bytes`); the caller still passes every input, output and the status word.
+ *   - limits: N <= KDA_NOALLOC_MAX_SEQS and H <= KDA_NOALLOC_MAX_HEADS, else KDA_ERR_LIMIT (nothing is launched);
+ *     the array takes about 1.1 MB of every GPU that loads the library, until the process exits;
+ *   - the first call on a device looks the array's device address up (once per device, with that device current);
+ *     make that first call outside stream capture;
+ *   - all calls on a device share the array, and it keeps the previous call's contents.  Nothing in it has to start at
+ *     zero (the planner rewrites every entry a call later reads), but two calls whose kernels overlap on the GPU
+ *     (different streams) race on it: serialise them;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * This entry point has no counterpart in the reference, whose launches own scratch tensors allocated by torch. */
+#define KDA_NOALLOC_MAX_SEQS 64
+#define KDA_NOALLOC_MAX_HEADS 16
+int kda_prefill_launch_noalloc(const KdaPrefillArgs* args, void* stream);
+
 /* ---- context parallelism: per-segment affine state maps (value-first orientation)
  *        S_end = S_in @ P + S_loc          out_t = o_loc_t + S_in applied to Qt_t
  * One call runs, for each of `n_seg` token segments [seg_t0[i], seg_t1[i]) and each head, chain L (S0 = 0, real v:
