@@ -173,6 +173,68 @@ def run_reference(args, lens):
     return 0
 
 
+def run_longctx(args, world, rank, dev, kda_b200):
+    """configs[3]: one sequence of 131072 tokens, H = 96, slow decay g = logsigmoid(N(2,1)), zero initial state; the
+    tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up."""
+    import torch.distributed as dist
+    from kda_b200 import parallel
+    T_total, H = 131072, 96
+    T = T_total // world
+    gen = torch.Generator(device=dev).manual_seed(200 + rank)
+    q = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    v = torch.randn(1, T, H, D, generator=gen, device=dev).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=dev) + 2.0)
+    beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=dev))
+    pieces = args.pieces or (1 if world == 1 else 2)
+    be = parallel.CudaBackend()
+
+    def step():
+        return parallel.context_parallel_prefill(q, k, v, g, beta, None, None, D ** -0.5, None, pieces=pieces, raw=False, backend=be)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        out, fin = step()
+    barrier()
+    sampler = ClockSampler(dev.index) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        out, fin = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    finite = bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(fin).all())
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        pk = peaks()
+        flops = T_total * H * FLOP_PER_TOKEN_HEAD
+        algo_bytes = T_total * H * BYTES_PER_TOKEN_HEAD + H * 2 * D * D * 4
+        print(json.dumps({
+            "metric": "KDA prefill tokens/s (H=96,K=V=128, one 131072-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[3]: T=131072, H=96, g=logsigmoid(N(2,1)), zero initial state", "pieces_per_rank": pieces,
+                       "parallelism": f"cp{world}", "finite": finite},
+            "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
+            "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
+                       "frac": flops / (ms * 1e-3) / 1e12 / pk["tf"]},
+            "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,6 +244,10 @@ def main(argv=None):
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
+    ap.add_argument("--workload", default="serving", choices=["serving", "longctx"],
+                    help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
+                         "sequence at H=96, context-parallel over the ranks")
+    ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = 1 on one GPU, else 2)")
     args = ap.parse_args(argv)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     lens = workload_lengths()
@@ -202,6 +268,8 @@ def main(argv=None):
         dist.init_process_group("nccl", device_id=dev)
     import kda_b200
 
+    if args.workload == "longctx":
+        return run_longctx(args, world, rank, dev, kda_b200)
     assert H_TOTAL % world == 0
     H = H_TOTAL // world
     T, N = sum(lens), len(lens)
