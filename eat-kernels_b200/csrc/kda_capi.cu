@@ -83,6 +83,24 @@ void fill_chunk_params(kda::ChunkParams& p, const KdaPrefillArgs* a) {
   p.status = a->status;
 }
 
+// Tensor maps of the token tensors for the tcgen05 kernel's copy engine (q, k, v in 64-channel halves with the 128-byte
+// swizzle, g as whole 128-channel rows).  T == 0: nothing is ever copied, the maps stay zeroed.
+int fill_tma_maps(kda::TmaMaps& m, const KdaPrefillArgs* a) {
+  memset(&m, 0, sizeof(m));
+  if (a->T <= 0) return KDA_OK;
+  if (a->T > 0x7fffffffLL) return KDA_ERR_LIMIT;
+  const bool plain = a->frontend == KDA_FRONTEND_PLAIN;
+  int rc = kda::encode_token_map(&m.q, a->q, 2, false, a->T, a->H, a->ldq, 64, true);
+  if (rc == 0) rc = kda::encode_token_map(&m.k, a->k, 2, false, a->T, a->H, a->ldk, 64, true);
+  if (rc == 0) rc = kda::encode_token_map(&m.v, a->v, 2, false, a->T, a->H, a->ldv, 64, true);
+  if (rc == 0) rc = kda::encode_token_map(&m.g, a->g, plain ? 4 : 2, plain, a->T, a->H, a->ldg, 128, false);
+  if (rc != 0) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (%d)", rc);
+    return KDA_ERR_LAUNCH;
+  }
+  return KDA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -132,7 +150,14 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   p.ck_row_stride = (long long)a->H * kda::STATE_ELEMS;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
-  e = a->kernel == KDA_KERNEL_MMA_SYNC ? kda::launch_chunk_fwd(p, a->N, stream) : kda::launch_chunk_umma(p, a->N, stream);
+  if (a->kernel == KDA_KERNEL_MMA_SYNC) {
+    e = kda::launch_chunk_fwd(p, a->N, stream);
+  } else {
+    kda::TmaMaps maps;
+    rc = fill_tma_maps(maps, a);
+    if (rc != KDA_OK) return rc;
+    e = kda::launch_chunk_umma(p, maps, a->N, stream);
+  }
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;
 }
@@ -198,8 +223,14 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   p.key_first = 0;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
-  e = a->kernel == KDA_KERNEL_MMA_SYNC ? kda::launch_chunk_fwd(p, 2 * s->n_seg, stream)
-                                       : kda::launch_chunk_umma(p, 2 * s->n_seg, stream);
+  if (a->kernel == KDA_KERNEL_MMA_SYNC) {
+    e = kda::launch_chunk_fwd(p, 2 * s->n_seg, stream);
+  } else {
+    kda::TmaMaps maps;
+    rc = fill_tma_maps(maps, a);
+    if (rc != KDA_OK) return rc;
+    e = kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream);
+  }
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;
 }

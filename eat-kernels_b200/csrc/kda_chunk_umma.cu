@@ -15,14 +15,15 @@
 // thread's issue path.  Because tf32 operands keep 10 mantissa bits, the state enters the products more accurately
 // than a bf16 copy would.
 //
-// Warp roles (20 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (cp.async of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
-// checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-19 operand preparation (gate + cumsum, L2 norm,
-// decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
+// Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
+// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
+// checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-27 operand preparation in two groups of eight
+// warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
 // (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
 // code in status[2].
 #include "kda_common.cuh"
 #include "kda_plan.cuh"
+#include "kda_tma.cuh"
 #include "kda_umma.cuh"
 
 namespace kda {
@@ -30,33 +31,34 @@ using namespace umma;
 
 namespace u {
 
-constexpr int WARPS = 20;
+constexpr int WARPS = 28;
 constexpr int THREADS = WARPS * 32;
 constexpr int W_MMA = 0, W_INV0 = 1, W_LOAD = 3, W_SCALE0 = 4, W_EPI0 = 8, W_PREP0 = 12;
-constexpr int PREP_WARPS = 8, PREP_THREADS = 256;
+constexpr int PREP_GROUPS = 2;                 // group g prepares the chunks c with c % 2 == g, in stage g
+constexpr int PREP_WARPS = 8, PREP_THREADS = 256;   // per group
 
 // ---- shared memory map (bytes); operand tiles are 1024-byte aligned
 constexpr int CS_KDQD = 0, CS_KR = 32768, CS_V = 49152, CS_TB = 57344, CS_M = 61440, CS_STAGE = 65536;
 constexpr int OFF_CONS = 0;                                   // 2 stages
 constexpr int RAW_G = 0, RAW_Q = 16384, RAW_K = 24576, RAW_STAGE = 32768;
 constexpr int OFF_RAW = OFF_CONS + 2 * CS_STAGE;              // 2 stages
-constexpr int OFF_KIS = OFF_RAW + 2 * RAW_STAGE;              // 8192
-constexpr int OFF_TBH = OFF_KIS + 8192;                       // 2 x 2048 (bf16, 64-byte swizzle)
+constexpr int OFF_KIS = OFF_RAW + 2 * RAW_STAGE;              // 2 x 8192 (one per prep group)
+constexpr int OFF_TBH = OFF_KIS + 2 * 8192;                   // 2 x 2048 (bf16, 64-byte swizzle)
 constexpr int OFF_L = OFF_TBH + 4096;                         // 2 x 4096 fp32 [32][32]
-constexpr int OFF_DEC = OFF_L + 8192;                         // 2 x 512
-constexpr int OFF_FR = OFF_DEC + 1024;                        // r, 2^r : 2 x 512
-constexpr int OFF_TOT = OFF_FR + 1024;                        // 512
-constexpr int OFF_BETA = OFF_TOT + 512;                       // raw-stage beta: 2 x 128
+constexpr int OFF_DEC = OFF_L + 8192;                         // 4 x 512 (a slot is rewritten four chunks later)
+constexpr int OFF_FR = OFF_DEC + 2048;                        // per prep group: r, 2^r, 2^(G31-r) : 2 x 3 x 512
+constexpr int OFF_BETA = OFF_FR + 2 * 1536;                   // raw-stage beta: 2 x 128
 constexpr int OFF_LBETA = OFF_BETA + 256;                     // beta next to L: 2 x 128
 constexpr int OFF_BAR = OFF_LBETA + 256;                      // mbarriers
-constexpr int NUM_BARS = 24;
+constexpr int NUM_BARS = 32;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem slot, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 64;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 // mbarrier indices
-constexpr int B_RAW_FULL = 0, B_RAW_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
-              B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20;
+constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
+              B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20, B_V_EMPTY = 21,
+              B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29;
 
 // tensor-memory columns
 constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
@@ -72,6 +74,15 @@ constexpr int E_LOAD = 0x10, E_PREP = 0x20, E_INV = 0x30, E_MMA = 0x40, E_SCALE 
 #define PROF_BEGIN do { } while (0)
 #endif
 
+// Byte offset of element (row, col) of a raw / decayed bf16 [32][128] tile as the copy engine lays it out with the
+// 128-byte swizzle: two halves of 64 channels, each 32 rows of 128 bytes, 16-byte chunks XOR-ed with (row % 8).
+// ldmatrix phases (8 rows, one chunk) are bank-conflict free in this layout.
+__device__ __forceinline__ uint32_t rawtile_off(int row, int col) {
+  return (uint32_t)((col >> 6) * 4096 + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + ((col & 7) << 1));
+}
+
+constexpr unsigned kSleepNs = 32;   // back-off of waiting warps (not of the MMA issuer)
+
 struct Ctx {
   uint8_t* smem;
   uint32_t bars;              // shared address of barrier 0
@@ -83,124 +94,117 @@ struct Ctx {
   unsigned long long* prof;   // [role 0..7][barrier 0..23 | 24 = total] cycle counters of CTA 0 (profiling builds only)
   __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const {
     const long long t = clock64();
-    mbar_wait(bar(i), parity, abort_flag, code + i);
+    mbar_wait(bar(i), parity, abort_flag, code + i, kSleepNs);
     if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 32 + i), (unsigned long long)(clock64() - t));
   }
 #else
-  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
+  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i, kSleepNs); }
 #endif
   // for a single elected thread (the MMA issuer)
   __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
 };
 
 // ------------------------------------------------------------------------------------------------ loader warp
-__device__ __forceinline__ void loader_issue(const ChunkParams& p, const Ctx& x, int c, int lane) {
-  const int rs = c & 1;
-  const int nvalid = min(C, x.len - c * C);
-  const long long tok0 = x.t0 + (long long)c * C;
-  uint8_t* raw = x.smem + OFF_RAW + rs * RAW_STAGE;
-  const uint32_t graw = smem_u32(raw + RAW_G), qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
-  const uint32_t vdst = smem_u32(x.smem + OFF_CONS + rs * CS_STAGE + CS_V);
-  if (p.frontend == 1) {
-    const float* g = reinterpret_cast<const float*>(p.g);
-#pragma unroll 4
-    for (int j = 0; j < 32; j++) {
-      const int idx = lane + 32 * j, row = idx >> 5, ch = idx & 31;
-      const bool ok = row < nvalid;
-      cp_async16(graw + row * 512 + ch * 16, g + (tok0 + (ok ? row : 0)) * p.ldg + (long long)x.h * D + ch * 4, ok ? 16 : 0);
+// One elected lane drives the copy engine: per chunk it arms the stage's mbarrier with the byte count and issues the
+// tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
+// MN-major 128-byte-swizzled layout is exactly what the engine writes), plus L2 prefetches two chunks ahead.
+template <int FE>
+__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x) {   // one thread
+  // Three copy streams per stage, each gated by the release of its own buffer: g (free after step B of the chunk two
+  // back), q/k (free after step C) and v (free once MMA2 has read it), so every tile is requested as early as its
+  // buffer allows; L2 prefetches run two chunks ahead.
+  const uint32_t g_bytes = FE == 1 ? 16384u : 8192u;
+#pragma unroll 1
+  for (int c = 0; c < x.nchunks; c++) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    const int tok0 = (int)(x.t0 + (long long)c * C);
+    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+    const uint32_t graw = smem_u32(raw + RAW_G), qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
+    const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
+    x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
+    tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), g_bytes);
+    tma::load_3d(graw, &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
+    x.wait1(B_QK_EMPTY + s, par ^ 1, E_LOAD);
+    tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
+    tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+    tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+    tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+    tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+    x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
+    tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
+    tma::load_3d(vdst, &m.v, 0, x.h, tok0, x.bar(B_V_FULL + s));
+    tma::load_3d(vdst + 4096, &m.v, 64, x.h, tok0, x.bar(B_V_FULL + s));
+    if (c + 2 < x.nchunks) {
+      const int tn = tok0 + 2 * C;
+      tma::prefetch_3d(&m.g, 0, x.h, tn);
+      tma::prefetch_3d(&m.q, 0, x.h, tn);
+      tma::prefetch_3d(&m.q, 64, x.h, tn);
+      tma::prefetch_3d(&m.k, 0, x.h, tn);
+      tma::prefetch_3d(&m.k, 64, x.h, tn);
+      tma::prefetch_3d(&m.v, 0, x.h, tn);
+      tma::prefetch_3d(&m.v, 64, x.h, tn);
     }
-  } else {
-    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.g);
-#pragma unroll 4
-    for (int j = 0; j < 16; j++) {
-      const int idx = lane + 32 * j, row = idx >> 4, ch = idx & 15;
-      const bool ok = row < nvalid;
-      cp_async16(graw + row * 256 + ch * 16, g + (tok0 + (ok ? row : 0)) * p.ldg + (long long)x.h * D + ch * 8, ok ? 16 : 0);
-    }
-  }
-#pragma unroll 4
-  for (int j = 0; j < 16; j++) {
-    const int idx = lane + 32 * j, row = idx >> 4, ch = idx & 15;
-    const bool ok = row < nvalid;
-    const long long tok = tok0 + (ok ? row : 0);
-    const int n = ok ? 16 : 0;
-    const uint32_t sw = (uint32_t)(row * 256 + ((ch ^ (row & 7)) << 4));
-    cp_async16(qraw + sw, p.q + tok * p.ldq + (long long)x.h * D + ch * 8, n);
-    cp_async16(kraw + sw, p.k + tok * p.ldk + (long long)x.h * D + ch * 8, n);
-    // v: A operand of MMA2 (M = value index, K = token), MN-major, 64 values per 128-byte row
-    cp_async16(vdst + mnmajor_b16_off(ch * 8, row, 4096, 1024), p.v + tok * p.ldv + (long long)x.h * D + ch * 8, n);
   }
 }
 
+template <int FE>
 __device__ __forceinline__ float load_beta(const ChunkParams& p, const Ctx& x, int c, int row) {
   const int nvalid = min(C, x.len - c * C);
   if (row >= nvalid) return 0.0f;
   const long long tok = x.t0 + (long long)c * C + row;
-  if (p.frontend == 1) return reinterpret_cast<const float*>(p.beta)[tok * p.ldbeta + x.h];
+  if (FE == 1) return reinterpret_cast<const float*>(p.beta)[tok * p.ldbeta + x.h];
   return sigmoidf_rel(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.beta)[tok * p.ldbeta + x.h]));
 }
 
-__device__ void role_loader(const ChunkParams& p, const Ctx& x, int lane, bool v_zero) {
-  float beta_next = x.nchunks > 0 ? load_beta(p, x, 0, lane) : 0.0f;
-  for (int c = 0; c < x.nchunks; c++) {
-    const int s = c & 1;
-    const uint32_t par = (uint32_t)((c >> 1) & 1);
-    x.wait(B_RAW_EMPTY + s, par ^ 1, E_LOAD);
-    x.wait(B_CONS_EMPTY + s, par ^ 1, E_LOAD);
-    PROF_BEGIN;
-    loader_issue(p, x, c, lane);
-    PROF_STAMP(1, 26);
-    reinterpret_cast<float*>(x.smem + OFF_BETA)[s * 32 + lane] = beta_next;
-    if (c + 1 < x.nchunks) beta_next = load_beta(p, x, c + 1, lane);
-    cp_async_commit();
-    PROF_STAMP(1, 27);
-    if (c > 0) {
-      cp_async_wait<1>();
-      PROF_STAMP(1, 28);
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(x.bar(B_RAW_FULL + ((c - 1) & 1)));
-    }
-  }
-  if (x.nchunks > 0) {
-    cp_async_wait<0>();
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(x.bar(B_RAW_FULL + ((x.nchunks - 1) & 1)));
-  }
-  (void)v_zero;
-}
-
 // ------------------------------------------------------------------------------------------------ prep warps
-__device__ __forceinline__ void prep_bar() { named_bar_sync(1, PREP_THREADS); }
-
-__device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_zero) {
+template <int FE>
+__device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid) {
   const int pw = ptid >> 5, lane = ptid & 31;
   const int ch = ptid & 127, half = ptid >> 7;
+  const int s = grp;                                   // the group's raw and consumer stage
+  const int bar_id = 1 + grp;
   float eA = 0.0f, dtb = 0.0f;
-  if (p.frontend == 0) {
+  if (FE == 0) {
     eA = __expf(p.A_log[x.h]);
     dtb = p.dt_bias[x.h * D + ch];
   }
-  float* fr = reinterpret_cast<float*>(x.smem + OFF_FR);
+  float* fr = reinterpret_cast<float*>(x.smem + OFF_FR) + grp * 3 * D;
   float* fer = fr + D;
-  float* tot = reinterpret_cast<float*>(x.smem + OFF_TOT);
-  for (int c = 0; c < x.nchunks; c++) {
-    const int s = c & 1;
+  float* tot = fr + 2 * D;
+  uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+  uint8_t* cons = x.smem + OFF_CONS + s * CS_STAGE;
+  uint8_t* kis_tile = x.smem + OFF_KIS + grp * 8192;
+  float* Gsm = reinterpret_cast<float*>(raw + RAW_G);
+  float* beta_s = reinterpret_cast<float*>(x.smem + OFF_BETA) + s * 32;
+  float beta_next = (ptid < C && grp < x.nchunks) ? load_beta<FE>(p, x, grp, ptid) : 0.0f;   // one own chunk ahead
+#pragma unroll 1
+  for (int c = grp; c < x.nchunks; c += PREP_GROUPS) {
     const uint32_t par = (uint32_t)((c >> 1) & 1);
     const int nvalid = min(C, x.len - c * C);
-    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-    uint8_t* cons = x.smem + OFF_CONS + s * CS_STAGE;
-    float* Gsm = reinterpret_cast<float*>(raw + RAW_G);
-    float* dec = reinterpret_cast<float*>(x.smem + OFF_DEC) + s * D;
-    x.wait(B_RAW_FULL + s, par, E_PREP);
-    x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
+    float* dec = reinterpret_cast<float*>(x.smem + OFF_DEC) + (c & 3) * D;
+    x.wait(B_G_FULL + s, par, E_PREP);
     PROF_BEGIN;
+    if (nvalid < C) {
+      x.wait(B_V_FULL + s, par, E_PREP);
+      // last, partial chunk: the v rows past the end of the run hold another sequence's data (or worse): zero them so
+      // that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  Whole 128-byte lines.
+      for (int i = ptid; i < (C - nvalid) * 16; i += PREP_THREADS) {
+        const int row = nvalid + (i >> 4), piece = i & 15;
+        *reinterpret_cast<uint4*>(cons + CS_V + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    if (ptid < C) {
+      beta_s[ptid] = beta_next;                        // read after the barriers of step A
+      if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
+    }
 
-    // ---- A: gate activation + inclusive cumulative log2-decay; two threads per channel, 16 tokens each
+    // ---- A: gate activation + inclusive cumulative log2-decay; two threads per channel, 16 tokens each.
+    // Touches only prep-private scratch (the decay slot c & 3 was last read four chunks ago), so it runs while the
+    // tensor core still works on older chunks.
     {
       float a[16];
-      if (p.frontend == 1) {
+      if (FE == 1) {
         const float* g = reinterpret_cast<const float*>(raw + RAW_G);
 #pragma unroll
         for (int i = 0; i < 16; i++) a[i] = g[(16 * half + i) * D + ch] * LOG2E;
@@ -216,7 +220,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
         if (i > 0) a[i] += a[i - 1];
       }
       if (half == 0) tot[ch] = a[15];
-      prep_bar();                       // all raw g values are in registers: G may now overwrite them in place
+      named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
       if (half == 1) {
         const float r = tot[ch];
 #pragma unroll
@@ -229,10 +233,14 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
 #pragma unroll
       for (int i = 0; i < 16; i++) Gsm[(16 * half + i) * D + ch] = a[i];
     }
-    prep_bar();
+    named_bar_sync(bar_id, PREP_THREADS);
     PROF_STAMP(2, 26);
 
-    // ---- B: L2 norm and decayed operand tiles; a warp owns 4 tokens, a lane 4 channels
+    // ---- B: L2 norm and decayed operand tiles; a warp owns 4 tokens, a lane 4 channels.  [kd ; qd] is written as
+    // soon as MMA1 of the chunk two back has read the stage; kr waits in registers until MMA3 has released the rest.
+    x.wait(B_QK_FULL + s, par, E_PREP);
+    x.wait(B_KDQD_EMPTY + s, par ^ 1, E_PREP);
+    float krr[4][4];
     {
       const float4 r4 = *reinterpret_cast<const float4*>(fr + 4 * lane);
       const float4 er4 = *reinterpret_cast<const float4*>(fer + 4 * lane);
@@ -243,13 +251,14 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
 #pragma unroll
       for (int tt = 0; tt < 4; tt++) {
         const int tok = 4 * pw + tt;
-        const uint32_t off = tile128_off(tok, 4 * lane);
-        const uint2 q2 = *reinterpret_cast<const uint2*>(raw + RAW_Q + off);
-        const uint2 k2 = *reinterpret_cast<const uint2*>(raw + RAW_K + off);
+        const uint32_t off = rawtile_off(tok, 4 * lane);
+        uint2 q2 = *reinterpret_cast<const uint2*>(raw + RAW_Q + off);
+        uint2 k2 = *reinterpret_cast<const uint2*>(raw + RAW_K + off);
+        if (tok >= nvalid) { q2 = make_uint2(0u, 0u); k2 = make_uint2(0u, 0u); }   // rows of the next sequence
         const float qf[4] = {bf16_lo(q2.x), bf16_hi(q2.x), bf16_lo(q2.y), bf16_hi(q2.y)};
         const float kf[4] = {bf16_lo(k2.x), bf16_hi(k2.x), bf16_lo(k2.y), bf16_hi(k2.y)};
         float qinv = p.scale, kinv = 1.0f;
-        if (p.frontend == 0) {
+        if (FE == 0) {
           float sq = qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3];
           float sk = kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3];
 #pragma unroll
@@ -262,33 +271,35 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
         }
         const float4 G4 = *reinterpret_cast<const float4*>(Gsm + tok * D + 4 * lane);
         const float Gv[4] = {G4.x, G4.y, G4.z, G4.w};
-        float kds[4], qds[4], kis[4], kdt[4], qdt[4], krr[4];
+        float kds[4], qds[4], kis[4], kdt[4], qdt[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           const float e = fminf(fmaxf(Gv[j] - rr[j], -126.0f), 126.0f);
           const float E = ex2f(e), Ei = ex2f(-e);
           const float kn = kf[j] * kinv, qn = qf[j] * qinv;
           kds[j] = kn * E; qds[j] = qn * E; kis[j] = kn * Ei;
-          kdt[j] = kds[j] * er[j]; qdt[j] = qds[j] * er[j]; krr[j] = kis[j] * elr[j];
+          kdt[j] = kds[j] * er[j]; qdt[j] = qds[j] * er[j]; krr[tt][j] = kis[j] * elr[j];
         }
         // in place: the decayed bf16 tiles of the intra-chunk products replace the raw q / k tiles
         *reinterpret_cast<uint2*>(raw + RAW_K + off) = make_uint2(pack_bf16(kds[0], kds[1]), pack_bf16(kds[2], kds[3]));
         *reinterpret_cast<uint2*>(raw + RAW_Q + off) = make_uint2(pack_bf16(qds[0], qds[1]), pack_bf16(qds[2], qds[3]));
-        *reinterpret_cast<uint2*>(x.smem + OFF_KIS + off) = make_uint2(pack_bf16(kis[0], kis[1]), pack_bf16(kis[2], kis[3]));
-        // tf32 operands of the state products: [kd ; qd] K-major (row = token / 32 + token), kr MN-major
+        *reinterpret_cast<uint2*>(kis_tile + off) = make_uint2(pack_bf16(kis[0], kis[1]), pack_bf16(kis[2], kis[3]));
+        // tf32 operands of the state products: [kd ; qd] K-major (row = token, 32 + token), kr MN-major
         *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(tok, 4 * lane, 8192)) = make_float4(kdt[0], kdt[1], kdt[2], kdt[3]);
         *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(32 + tok, 4 * lane, 8192)) = make_float4(qdt[0], qdt[1], qdt[2], qdt[3]);
-        *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, tok, 512, 2048)) = make_float4(krr[0], krr[1], krr[2], krr[3]);
       }
     }
     PROF_STAMP(2, 27);
-    prep_bar();
+    fence_proxy_async();                                  // this thread's reads / writes of the g region precede its refill
+    named_bar_sync(bar_id, PREP_THREADS);
+    if (lane == 0) mbar_arrive(x.bar(B_G_EMPTY + s));     // the gate tile may be refilled: step C does not read it
     PROF_STAMP(2, 28);
 
     // ---- C: one 16x16 block of A = kd' ki'^T (warps 0-3) or M = qd' ki'^T (warps 4-7) per warp
     {
       const int which = pw >> 2, rb = (pw >> 1) & 1, cb = pw & 1;
-      const float* beta_s = reinterpret_cast<const float*>(x.smem + OFF_BETA) + s * 32;
+      const int g = lane >> 2, t = lane & 3;
+      const int i0 = 16 * rb + g, i1 = i0 + 8;
       float acc[2][4];
 #pragma unroll
       for (int i = 0; i < 2; i++)
@@ -296,20 +307,18 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
       if (!(rb == 0 && cb == 1)) {
         const uint32_t a_tile = smem_u32(raw + (which ? RAW_Q : RAW_K));
-        const uint32_t b_tile = smem_u32(x.smem + OFF_KIS);
+        const uint32_t b_tile = smem_u32(kis_tile);
         const int a_row = 16 * rb + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int b_row = 16 * cb + 8 * (lane >> 4) + (lane & 7);
 #pragma unroll
         for (int kt = 0; kt < 8; kt++) {
           uint32_t a[4], b[4];
-          ldmatrix_x4(a, a_tile + tile128_off(a_row, (2 * kt + (lane >> 4)) * 8));
-          ldmatrix_x4(b, b_tile + tile128_off(b_row, (2 * kt + ((lane >> 3) & 1)) * 8));
+          ldmatrix_x4(a, a_tile + rawtile_off(a_row, (2 * kt + (lane >> 4)) * 8));
+          ldmatrix_x4(b, b_tile + rawtile_off(b_row, (2 * kt + ((lane >> 3) & 1)) * 8));
           mma_bf16(acc[0], a, b[0], b[1]);
           mma_bf16(acc[1], a, b[2], b[3]);
         }
       }
-      const int g = lane >> 2, t = lane & 3;
-      const int i0 = 16 * rb + g, i1 = i0 + 8;
       if (which == 0) {
         x.wait(B_L_EMPTY + s, par ^ 1, E_PREP);
         float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
@@ -321,7 +330,16 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
           *reinterpret_cast<float2*>(Lsm + i1 * C + j) = make_float2((j < i1) ? acc[nt][2] * b1 : 0.0f, (j + 1 < i1) ? acc[nt][3] * b1 : 0.0f);
         }
         if (pw == 0) reinterpret_cast<float*>(x.smem + OFF_LBETA)[s * 32 + lane] = beta_s[lane];
-      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x.bar(B_L_FULL + s));      // the inverse of this chunk may start
+      }
+      // ---- D: the operands of MMA3 go out once the tensor core has released the rest of the stage
+      x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
+#pragma unroll
+      for (int tt = 0; tt < 4; tt++)
+        *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, 4 * pw + tt, 512, 2048)) =
+            make_float4(krr[tt][0], krr[tt][1], krr[tt][2], krr[tt][3]);
+      if (which == 1) {
 #pragma unroll
         for (int nt = 0; nt < 2; nt++) {
           const int j = 16 * cb + 8 * nt + 2 * t;
@@ -337,45 +355,100 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int ptid, bool v_z
     __syncwarp();
     if (lane == 0) {
       mbar_arrive(x.bar(B_P1_FULL + s));
-      mbar_arrive(x.bar(B_L_FULL + s));
-      mbar_arrive(x.bar(B_RAW_EMPTY + s));
+      mbar_arrive(x.bar(B_QK_EMPTY + s));        // the q / k tiles are no longer read
     }
   }
-  (void)v_zero;
 }
 
 // ------------------------------------------------------------------------------------------------ inverse warps
+// T = (I + L)^-1 for the strictly lower triangular fp32 L [32][32] of a chunk, in place in L's buffer, by one warp:
+//   1. the two 16x16 diagonal blocks by forward substitution in fp32 registers, one half-warp per block, lane = column
+//      (16 dependent rows instead of 32);
+//   2. the off-diagonal block T10 = -T11 (L10 T00) as two 16x16x16 products on mma.sync (tf32 operands, fp32
+//      accumulation; T is consumed as a tf32 / bf16 tensor-core operand anyway).
+// Then Tb = T diag(beta) goes out as the tf32 and bf16 operand tiles of MMA2.
+__device__ __forceinline__ void mm16_tf32(float (&acc)[2][4], const float* A, const float* B, int lane) {
+  // acc[nt] (16 x 8) += A[16][16] * B[16][16], both row-major with a row stride of 32 floats
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int kt = 0; kt < 2; kt++) {
+    const uint32_t a[4] = {__float_as_uint(A[g * C + 8 * kt + t]), __float_as_uint(A[(g + 8) * C + 8 * kt + t]),
+                           __float_as_uint(A[g * C + 8 * kt + t + 4]), __float_as_uint(A[(g + 8) * C + 8 * kt + t + 4])};
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+      mma_tf32(acc[nt], a, __float_as_uint(B[(8 * kt + t) * C + 8 * nt + g]), __float_as_uint(B[(8 * kt + t + 4) * C + 8 * nt + g]));
+  }
+}
+
 __device__ void role_inverse(const Ctx& x, int which, int lane) {
+  const int blk = lane >> 4, cl = lane & 15;
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll 1
   for (int c = which; c < x.nchunks; c += 2) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
     x.wait(B_L_FULL + s, par, E_INV);
-    const float* Lsm = reinterpret_cast<const float*>(x.smem + OFF_L) + s * 1024;
+    float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
     PROF_BEGIN;
-    float Tc[C];
+    // ---- 1: diagonal blocks
+    {
+      const float* Lb = Lsm + blk * 16 * C + blk * 16;
+      float Tc[16];
 #pragma unroll
-    for (int i = 0; i < C; i++) {
-      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+      for (int i = 0; i < 16; i++) {
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-      for (int j = 0; j + 3 < i; j += 4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(Lsm + i * C + j);
-        a0 = fmaf(l4.x, Tc[j], a0);
-        a1 = fmaf(l4.y, Tc[j + 1], a1);
-        a2 = fmaf(l4.z, Tc[j + 2], a2);
-        a3 = fmaf(l4.w, Tc[j + 3], a3);
+        for (int j = 0; j + 3 < i; j += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(Lb + i * C + j);
+          a0 = fmaf(l4.x, Tc[j], a0);
+          a1 = fmaf(l4.y, Tc[j + 1], a1);
+          a2 = fmaf(l4.z, Tc[j + 2], a2);
+          a3 = fmaf(l4.w, Tc[j + 3], a3);
+        }
+#pragma unroll
+        for (int j = i & ~3; j < i; j++) a0 = fmaf(Lb[i * C + j], Tc[j], a0);
+        Tc[i] = ((i == cl) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
       }
+      __syncwarp();                                   // every lane has read its diagonal block
+      float* Tb_ = Lsm + blk * 16 * C + blk * 16;
 #pragma unroll
-      for (int j = i & ~3; j < i; j++) a0 = fmaf(Lsm[i * C + j], Tc[j], a0);
-      Tc[i] = ((i == lane) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
+      for (int i = 0; i < 16; i++) Tb_[i * C + cl] = Tc[i];
     }
+    __syncwarp();
+    // ---- 2: T10 = -T11 (L10 T00), in place in the (1,0) block
+    {
+      float* L10 = Lsm + 16 * C;
+      float acc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+      mm16_tf32(acc, L10, Lsm, lane);                 // X = L10 T00
+      __syncwarp();                                   // L10 fully read
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) {
+        *reinterpret_cast<float2*>(L10 + g * C + 8 * nt + 2 * t) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(L10 + (g + 8) * C + 8 * nt + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+      }
+      __syncwarp();
+      mm16_tf32(acc, Lsm + 16 * C + 16, L10, lane);   // T11 X
+      __syncwarp();                                   // X fully read
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) {
+        *reinterpret_cast<float2*>(L10 + g * C + 8 * nt + 2 * t) = make_float2(-acc[nt][0], -acc[nt][1]);
+        *reinterpret_cast<float2*>(L10 + (g + 8) * C + 8 * nt + 2 * t) = make_float2(-acc[nt][2], -acc[nt][3]);
+      }
+    }
+    __syncwarp();
     const float bc = reinterpret_cast<const float*>(x.smem + OFF_LBETA)[s * 32 + lane];
     PROF_STAMP(3, 26);
     x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
     uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
     uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
-#pragma unroll
+#pragma unroll 4
     for (int i = 0; i < C; i++) {
-      const float val = Tc[i] * bc;
+      const float val = Lsm[i * C + lane] * bc;
       *reinterpret_cast<float*>(tb + kmajor_f32_off(i, lane, 0)) = val;
       *reinterpret_cast<__nv_bfloat16*>(tbh + kmajor_b16_sw64_off(i, lane)) = __float2bfloat16_rn(val);
     }
@@ -398,6 +471,7 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
   constexpr uint32_t ID3B = make_idesc(FMT_TF32, 128, 32, 0, 0, 0);
   const uint32_t tS = tmem + TM_S, tU = tmem + TM_U;
   x.wait1(B_S_READY, 0, E_MMA);                    // initial state is in tensor memory
+#pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
@@ -410,7 +484,10 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
     for (int ks = 0; ks < 16; ks++)
       mma_ts_tf32(tWO, tS + 8 * ks, make_sdesc(cons + CS_KDQD + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, LAYOUT_SW128), ID1, ks > 0);
     mma_commit(x.bar(B_MMA1_DONE));
+    mma_commit(x.bar(B_KDQD_EMPTY + s));                  // [kd ; qd] of this stage may be rewritten
     x.wait1(B_INV_FULL + s, par, E_MMA);
+    tc_fence_after();
+    x.wait1(B_V_FULL + s, par, E_MMA);
     tc_fence_after();
     if (!v_zero) {
 #pragma unroll
@@ -421,6 +498,7 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
       mma_ts_tf32(tU, tWO + 8 * ks, make_sdesc(cons + CS_TB + ks * 32, 16, 1024, LAYOUT_SW128), ID2B, (ks > 0) || !v_zero);
+    mma_commit(x.bar(B_V_EMPTY + s));                     // the v tile may be refilled once MMA2 has read it
     x.wait1(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA);   // scaler finished St <- St diag(2^G31)
     tc_fence_after();
 #pragma unroll
@@ -467,6 +545,7 @@ __device__ __forceinline__ void store_row_piece<__nv_bfloat16>(__nv_bfloat16* ds
   }
 }
 
+template <int KF>
 __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
   const int v = 32 * quarter + lane;
   const uint32_t tS = tmem + TM_S + ((uint32_t)(32 * quarter) << 16);
@@ -480,7 +559,7 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
       for (int i = 0; i < 32; i++) r[i] = __float_as_uint((32 * j + i == v) ? one : 0.0f);
     } else {
       const float* src = task.src + (size_t)x.h * STATE_ELEMS;
-      if (!p.key_first) {
+      if (!KF) {
         const float4* s4 = reinterpret_cast<const float4*>(src + v * D + 32 * j);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -499,12 +578,13 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
   __syncwarp();
   if (lane == 0) mbar_arrive(x.bar(B_S_READY));
 
+#pragma unroll 1
   for (int c = 0; c <= x.nchunks; c++) {
     x.wait(B_MMA1_DONE, (uint32_t)(c & 1), E_SCALE);
     tc_fence_after();
     const bool last = c == x.nchunks;
     const bool ck = !last && task.ck != nullptr && p.ck_every_chunks > 0 && (c % p.ck_every_chunks) == 0;
-    const float* dec = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 1) * D;
+    const float* dec = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 3) * D;
     long long ck_off = 0;
     if (ck) ck_off = (long long)(c / p.ck_every_chunks) * p.ck_row_stride + (long long)x.h * STATE_ELEMS;
 #pragma unroll 1
@@ -513,11 +593,11 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
       tmem_ld32(tS + 32 * j, r);
       tmem_wait_ld();
       if (ck) {
-        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, p.key_first, v, 32 * j, r);
-        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, p.key_first, v, 32 * j, r);
+        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, KF, v, 32 * j, r);
+        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, KF, v, 32 * j, r);
       }
       if (last) {
-        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, p.key_first, v, 32 * j, r);
+        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, KF, v, 32 * j, r);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -543,6 +623,7 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
 __device__ void role_epilogue(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
   const int v = 32 * quarter + lane;
   __nv_bfloat16* obase = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
+#pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
     const int s = c & 1;
     x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI);
@@ -564,7 +645,8 @@ __device__ void role_epilogue(const ChunkParams& p, const Task& task, const Ctx&
 }
 
 // ------------------------------------------------------------------------------------------------ kernel
-__global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p) {
+template <int FE, int KF>
+__global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int H = p.H;
@@ -614,12 +696,17 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   if (tid == 0) {
     *x.abort_flag = 0;
     for (int i = 0; i < 2; i++) {
-      mbar_init(x.bar(B_RAW_FULL + i), 1);
-      mbar_init(x.bar(B_RAW_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_G_FULL + i), 1);
+      mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_QK_FULL + i), 1);
+      mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_V_FULL + i), 1);
+      mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
       mbar_init(x.bar(B_CONS_EMPTY + i), 1);
       mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
       mbar_init(x.bar(B_INV_FULL + i), 1);
-      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS);
+      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
+      mbar_init(x.bar(B_V_EMPTY + i), 1);
       mbar_init(x.bar(B_L_EMPTY + i), 1);
       mbar_init(x.bar(B_O_FULL + i), 1);
       mbar_init(x.bar(B_O_EMPTY + i), 4);
@@ -645,13 +732,15 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);
   } else if (warp == W_LOAD) {
-    role_loader(p, x, lane, v_zero);
+    if (lane == 0) role_loader<FE>(p, maps, x);
+    __syncwarp();
   } else if (warp < W_EPI0) {
-    role_scaler(p, task, x, tmem, warp & 3, lane);
+    role_scaler<KF>(p, task, x, tmem, warp & 3, lane);
   } else if (warp < W_PREP0) {
     role_epilogue(p, task, x, tmem, warp & 3, lane);
   } else {
-    role_prep(p, x, tid - W_PREP0 * 32, v_zero);
+    const int pt = tid - W_PREP0 * 32;
+    role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
   }
 
 #ifdef KDA_PROF
@@ -669,18 +758,25 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
 
 }  // namespace u
 
-cudaError_t launch_chunk_umma(const ChunkParams& p, int n_task_cap, cudaStream_t stream) {
+cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream) {
+  // one instantiation per (front-end, state layout): smaller code per launch, and instruction-cache footprint is what
+  // bounds this role-specialised kernel
+  typedef void (*Kern)(const ChunkParams, const TmaMaps);
+  static const Kern kerns[2][2] = {{u::kda_chunk_umma_kernel<0, 0>, u::kda_chunk_umma_kernel<0, 1>},
+                                   {u::kda_chunk_umma_kernel<1, 0>, u::kda_chunk_umma_kernel<1, 1>}};
   static int attr_dev_mask = 0;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(attr_dev_mask & (1 << (dev & 31)))) {
-    cudaError_t e = cudaFuncSetAttribute(u::kda_chunk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, u::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
+    for (int i = 0; i < 4; i++) {
+      cudaError_t e = cudaFuncSetAttribute(kerns[i >> 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize, u::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+    }
     attr_dev_mask |= 1 << (dev & 31);
   }
   const long long blocks = (long long)n_task_cap * p.H;
   if (blocks <= 0) return cudaSuccess;
-  u::kda_chunk_umma_kernel<<<(unsigned)blocks, u::THREADS, u::SMEM_BYTES, stream>>>(p);
+  kerns[p.frontend ? 1 : 0][p.key_first ? 1 : 0]<<<(unsigned)blocks, u::THREADS, u::SMEM_BYTES, stream>>>(p, maps);
   return cudaGetLastError();
 }
 

@@ -1,6 +1,7 @@
 // Parameters of the device planner (see kda_plan.cu).
 #pragma once
 #include "kda_common.cuh"
+#include "kda_tma.cuh"
 
 namespace kda {
 
@@ -25,6 +26,6 @@ struct PlanParams {
 
 cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream);
 cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);    // mma.sync kernel
-cudaError_t launch_chunk_umma(const ChunkParams& p, int n_task_cap, cudaStream_t stream);   // tcgen05 kernel
+cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream);   // tcgen05 kernel
 
 }  // namespace kda

@@ -50,12 +50,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 // Bounded wait of ONE thread.  `abort_flag` is a shared-memory int; returns false when the wait was abandoned
-// (after kWaitLimitNs of wall time, or as soon as another thread of the CTA has given up).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+// (after kWaitLimitNs of wall time, or as soon as another thread of the CTA has given up).  `sleep_ns` > 0 makes the
+// waiter sleep between polls so that it does not take issue slots from the warps it is waiting for.
+// The polling loop is kept out of line: it is instantiated at dozens of wait sites, and instruction-cache footprint is
+// what limits the role-specialised kernels.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, unsigned sleep_ns) {
   unsigned long long t0 = 0;
   uint32_t n = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (*abort_flag != 0) return false;
     if ((++n & 255u) == 0) {
       const unsigned long long now = global_timer_ns();
@@ -67,6 +70,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, unsigned sleep_ns = 0) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, code, sleep_ns);
 }
 // Bounded wait of a converged warp: lane 0 waits, the other lanes sleep at the warp barrier and then observe the
 // completed phase themselves (one successful poll each), which gives every lane its own acquire.
