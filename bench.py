@@ -186,7 +186,7 @@ def run_longctx(args, world, rank, dev, kda_b200):
     v = torch.randn(1, T, H, D, generator=gen, device=dev).to(torch.bfloat16)
     g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=dev) + 2.0)
     beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=dev))
-    pieces = args.pieces or (1 if world == 1 else 2)
+    pieces = args.pieces or parallel.choose_pieces(T, H, rank == 0)
     be = parallel.CudaBackend()
 
     def step():
@@ -247,7 +247,7 @@ def main(argv=None):
     ap.add_argument("--workload", default="serving", choices=["serving", "longctx"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
-    ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = 1 on one GPU, else 2)")
+    ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = chosen by a wave model)")
     args = ap.parse_args(argv)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     lens = workload_lengths()

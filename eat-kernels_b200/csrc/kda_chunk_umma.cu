@@ -16,7 +16,7 @@
 // than a bf16 copy would.
 //
 // Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
+// 3 loader (three lanes drive the TMA copy streams g / q,k / v; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
 // checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-27 operand preparation in two groups of eight
 // warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
 // (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
@@ -81,7 +81,10 @@ __device__ __forceinline__ uint32_t rawtile_off(int row, int col) {
   return (uint32_t)((col >> 6) * 4096 + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + ((col & 7) << 1));
 }
 
-constexpr unsigned kSleepNs = 32;   // back-off of waiting warps (not of the MMA issuer)
+#ifndef KDA_SLEEP_NS
+#define KDA_SLEEP_NS 32
+#endif
+constexpr unsigned kSleepNs = KDA_SLEEP_NS;   // back-off of waiting warps (not of the MMA issuer)
 
 struct Ctx {
   uint8_t* smem;
@@ -92,13 +95,15 @@ struct Ctx {
   __device__ __forceinline__ uint32_t bar(int i) const { return bars + 8u * (uint32_t)i; }
 #ifdef KDA_PROF
   unsigned long long* prof;   // [role 0..7][barrier 0..23 | 24 = total] cycle counters of CTA 0 (profiling builds only)
-  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const {
+  __device__ __forceinline__ void wait(int i, uint32_t parity, int code, unsigned sleep_ns = kSleepNs) const {
     const long long t = clock64();
-    mbar_wait(bar(i), parity, abort_flag, code + i, kSleepNs);
+    mbar_wait(bar(i), parity, abort_flag, code + i, sleep_ns);
     if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 32 + i), (unsigned long long)(clock64() - t));
   }
 #else
-  __device__ __forceinline__ void wait(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i, kSleepNs); }
+  __device__ __forceinline__ void wait(int i, uint32_t parity, int code, unsigned sleep_ns = kSleepNs) const {
+    mbar_wait(bar(i), parity, abort_flag, code + i, sleep_ns);
+  }
 #endif
   // for a single elected thread (the MMA issuer)
   __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
@@ -109,41 +114,35 @@ struct Ctx {
 // tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
 // MN-major 128-byte-swizzled layout is exactly what the engine writes), plus L2 prefetches two chunks ahead.
 template <int FE>
-__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x) {   // one thread
-  // Three copy streams per stage, each gated by the release of its own buffer: g (free after step B of the chunk two
-  // back), q/k (free after step C) and v (free once MMA2 has read it), so every tile is requested as early as its
-  // buffer allows; L2 prefetches run two chunks ahead.
-  const uint32_t g_bytes = FE == 1 ? 16384u : 8192u;
+__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
+  // Three independent copy streams, one lane each, so that a late release of one buffer never delays the refill of
+  // another: lane 0 the gate tile (free after step B of the chunk two back), lane 1 q / k (free after step C), lane 2
+  // v (free once MMA2 has read it).  Each tile is requested as soon as its buffer allows.
+  if (lane > 2) return;
 #pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
     const int tok0 = (int)(x.t0 + (long long)c * C);
     uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-    const uint32_t graw = smem_u32(raw + RAW_G), qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
-    const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
-    x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
-    tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), g_bytes);
-    tma::load_3d(graw, &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
-    x.wait1(B_QK_EMPTY + s, par ^ 1, E_LOAD);
-    tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
-    tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-    tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
-    tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-    tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
-    x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
-    tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
-    tma::load_3d(vdst, &m.v, 0, x.h, tok0, x.bar(B_V_FULL + s));
-    tma::load_3d(vdst + 4096, &m.v, 64, x.h, tok0, x.bar(B_V_FULL + s));
-    if (c + 2 < x.nchunks) {
-      const int tn = tok0 + 2 * C;
-      tma::prefetch_3d(&m.g, 0, x.h, tn);
-      tma::prefetch_3d(&m.q, 0, x.h, tn);
-      tma::prefetch_3d(&m.q, 64, x.h, tn);
-      tma::prefetch_3d(&m.k, 0, x.h, tn);
-      tma::prefetch_3d(&m.k, 64, x.h, tn);
-      tma::prefetch_3d(&m.v, 0, x.h, tn);
-      tma::prefetch_3d(&m.v, 64, x.h, tn);
+    if (lane == 0) {
+      x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
+      tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), FE == 1 ? 16384u : 8192u);
+      tma::load_3d(smem_u32(raw + RAW_G), &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
+    } else if (lane == 1) {
+      const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
+      x.wait1(B_QK_EMPTY + s, par ^ 1, E_LOAD);
+      tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
+      tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+      tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+      tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+      tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+    } else {
+      const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
+      x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
+      tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
+      tma::load_3d(vdst, &m.v, 0, x.h, tok0, x.bar(B_V_FULL + s));
+      tma::load_3d(vdst + 4096, &m.v, 64, x.h, tok0, x.bar(B_V_FULL + s));
     }
   }
 }
@@ -273,12 +272,18 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         const float Gv[4] = {G4.x, G4.y, G4.z, G4.w};
         float kds[4], qds[4], kis[4], kdt[4], qdt[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const float e = fminf(fmaxf(Gv[j] - rr[j], -126.0f), 126.0f);
-          const float E = ex2f(e), Ei = ex2f(-e);
-          const float kn = kf[j] * kinv, qn = qf[j] * qinv;
-          kds[j] = kn * E; qds[j] = qn * E; kis[j] = kn * Ei;
-          kdt[j] = kds[j] * er[j]; qdt[j] = qds[j] * er[j]; krr[tt][j] = kis[j] * elr[j];
+        for (int j = 0; j < 4; j += 2) {               // channel pairs, packed fp32x2 arithmetic
+          const float e0 = fminf(fmaxf(Gv[j] - rr[j], -126.0f), 126.0f);
+          const float e1 = fminf(fmaxf(Gv[j + 1] - rr[j + 1], -126.0f), 126.0f);
+          const float2 E = make_float2(ex2f(e0), ex2f(e1)), Ei = make_float2(ex2f(-e0), ex2f(-e1));
+          float2 kn = make_float2(kf[j], kf[j + 1]);
+          if (FE == 0) kn = mul2(kn, make_float2(kinv, kinv));
+          const float2 qn = mul2(make_float2(qf[j], qf[j + 1]), make_float2(qinv, qinv));
+          const float2 kd2 = mul2(kn, E), qd2 = mul2(qn, E), ki2 = mul2(kn, Ei);
+          const float2 er2 = make_float2(er[j], er[j + 1]);
+          const float2 kt2 = mul2(kd2, er2), qt2 = mul2(qd2, er2), kr2 = mul2(ki2, make_float2(elr[j], elr[j + 1]));
+          kds[j] = kd2.x; kds[j + 1] = kd2.y; qds[j] = qd2.x; qds[j + 1] = qd2.y; kis[j] = ki2.x; kis[j + 1] = ki2.y;
+          kdt[j] = kt2.x; kdt[j + 1] = kt2.y; qdt[j] = qt2.x; qdt[j + 1] = qt2.y; krr[tt][j] = kr2.x; krr[tt][j + 1] = kr2.y;
         }
         // in place: the decayed bf16 tiles of the intra-chunk products replace the raw q / k tiles
         *reinterpret_cast<uint2*>(raw + RAW_K + off) = make_uint2(pack_bf16(kds[0], kds[1]), pack_bf16(kds[2], kds[3]));
@@ -602,10 +607,10 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const float4 d4 = *reinterpret_cast<const float4*>(dec + 32 * j + 4 * i);
-          r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) * d4.x);
-          r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * d4.y);
-          r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * d4.z);
-          r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * d4.w);
+          const float2 lo = mul2(make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), make_float2(d4.x, d4.y));
+          const float2 hi = mul2(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), make_float2(d4.z, d4.w));
+          r[4 * i] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
+          r[4 * i + 2] = __float_as_uint(hi.x); r[4 * i + 3] = __float_as_uint(hi.y);
         }
         tmem_st32(tS + 32 * j, r);
       }
@@ -626,7 +631,7 @@ __device__ void role_epilogue(const ChunkParams& p, const Task& task, const Ctx&
 #pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
     const int s = c & 1;
-    x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI);
+    x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI, 256);   // off the critical chain: poll rarely
     tc_fence_after();
     uint32_t r[32];
     tmem_ld32(tmem + TM_WO + 64 * s + 32 + ((uint32_t)(32 * quarter) << 16), r);
@@ -732,7 +737,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);
   } else if (warp == W_LOAD) {
-    if (lane == 0) role_loader<FE>(p, maps, x);
+    role_loader<FE>(p, maps, x, lane);
     __syncwarp();
   } else if (warp < W_EPI0) {
     role_scaler<KF>(p, task, x, tmem, warp & 3, lane);

@@ -56,6 +56,19 @@ def split_pieces(T, pieces):
     return bounds
 
 
+def choose_pieces(T, H, first_rank, n_sms=148, max_pieces=8):
+    """Pieces per rank that minimise the makespan of the segment launch in chunk steps: a mapped piece costs two CTAs
+    per head (chains L and Tr), the unmapped first piece of rank 0 one; CTAs run in waves of `n_sms`."""
+    nchunks = -(-T // CHUNK)
+    best, best_cost = 1, None
+    for p in range(1, max(1, min(max_pieces, nchunks)) + 1):
+        ctas = H * (2 * p - (1 if first_rank else 0))
+        cost = -(-ctas // n_sms) * -(-nchunks // p)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = p, cost
+    return best
+
+
 class CudaBackend:
     """The shipped backend: the three context-parallel steps on the current CUDA device through the C ABI."""
 
@@ -139,13 +152,14 @@ def compose_rank_map(backend, P, S_loc):
     return P_rank, L_rank
 
 
-def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_state=None, *, group=None, pieces=2,
+def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_state=None, *, group=None, pieces=0,
                              raw=True, backend=None):
     """Context-parallel prefill of ONE sequence whose tokens are sharded over the ranks of `group` in rank order.
 
     q, k, v, g [1, T_local, H, 128] and beta [1, T_local, H] are this rank's shard (contiguous token rows);
     initial_state [1, H, 128, 128] fp32 value-first is read on rank 0 (zeros when None).  With `group=None` (or a
-    single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.
+    single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.  `pieces=0` picks the
+    piece count per rank from a wave model of the segment launch (`choose_pieces`).
     Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank)."""
     import torch.distributed as dist
 
@@ -153,6 +167,8 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     rank = dist.get_rank(group) if world > 1 else 0
     backend = backend or CudaBackend()
     T, H = q.shape[1], q.shape[2]
+    if pieces <= 0:
+        pieces = choose_pieces(T, H, rank == 0)
     bounds = split_pieces(T, pieces)
     n = len(bounds) - 1
     need_map = [1] * n

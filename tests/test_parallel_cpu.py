@@ -104,6 +104,11 @@ def test_split_pieces_and_head_slice():
     assert s.shape == (2, 3, 2, 4) and torch.equal(s, t[:, :, 2:4])
     with pytest.raises(ValueError):
         parallel.head_slice(0, 3, t)
+    # wave model: rank 0 of a long H=96 sequence keeps one plain chain (96 CTAs, one wave); mapped ranks cut into
+    # three pieces (576 CTAs in four waves of a third of the chunks beat 192 CTAs in two waves of all of them)
+    assert parallel.choose_pieces(16384, 96, True) == 1
+    assert parallel.choose_pieces(16384, 96, False) == 3
+    assert parallel.choose_pieces(32, 4, False) == 1
 
 
 def _hp_worker(rank, world, port, ret):
