@@ -16,7 +16,7 @@
 // than a bf16 copy would.
 //
 // Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (three lanes drive the TMA copy streams g / q,k / v; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
+// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
 // checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-27 operand preparation in two groups of eight
 // warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
 // (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
@@ -67,7 +67,7 @@ constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
 constexpr int E_LOAD = 0x10, E_PREP = 0x20, E_INV = 0x30, E_MMA = 0x40, E_SCALE = 0x50, E_EPI = 0x60;
 
 #ifdef KDA_PROF
-#define PROF_STAMP(role, slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(x.prof + (role) * 32 + (slot), (unsigned long long)(_t - prof_last)); prof_last = _t; } } while (0)
+#define PROF_STAMP(role, slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) { const long long _t = clock64(); atomicAdd(x.prof + (role) * 64 + 32 + (slot), (unsigned long long)(_t - prof_last)); prof_last = _t; } } while (0)
 #define PROF_BEGIN long long prof_last = clock64()
 #else
 #define PROF_STAMP(role, slot) do { } while (0)
@@ -98,7 +98,7 @@ struct Ctx {
   __device__ __forceinline__ void wait(int i, uint32_t parity, int code, unsigned sleep_ns = kSleepNs) const {
     const long long t = clock64();
     mbar_wait(bar(i), parity, abort_flag, code + i, sleep_ns);
-    if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 32 + i), (unsigned long long)(clock64() - t));
+    if ((threadIdx.x & 31) == 0 && blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 64 + i), (unsigned long long)(clock64() - t));
   }
 #else
   __device__ __forceinline__ void wait(int i, uint32_t parity, int code, unsigned sleep_ns = kSleepNs) const {
@@ -106,7 +106,15 @@ struct Ctx {
   }
 #endif
   // for a single elected thread (the MMA issuer)
+#ifdef KDA_PROF
+  __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const {
+    const long long t = clock64();
+    mbar_wait(bar(i), parity, abort_flag, code + i);
+    if (blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 64 + i), (unsigned long long)(clock64() - t));
+  }
+#else
   __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
+#endif
 };
 
 // ------------------------------------------------------------------------------------------------ loader warp
@@ -114,30 +122,35 @@ struct Ctx {
 // tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
 // MN-major 128-byte-swizzled layout is exactly what the engine writes), plus L2 prefetches two chunks ahead.
 template <int FE>
-__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
-  // Three independent copy streams, one lane each, so that a late release of one buffer never delays the refill of
-  // another: lane 0 the gate tile (free after step B of the chunk two back), lane 1 q / k (free after step C), lane 2
-  // v (free once MMA2 has read it).  Each tile is requested as soon as its buffer allows.
-  if (lane > 2) return;
+__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x) {   // one thread
+  // One thread requests every tile of chunk c in the order the buffers come free: the gate tile (free after step B
+  // of chunk c-2), q / k (free after step C), v (free once MMA2 of chunk c-2 has read it).  Each tile has its own
+  // full / empty barrier pair, so consumers start on a tile as soon as it has landed.
+  // Requesting the tiles of later chunks without waiting for the v buffer (separate lanes per stream, or v deferred by
+  // one chunk) was tried: it let the preparation run further ahead of the tensor core and produced intermittent
+  // mismatches on hardware that reading the hand-offs did not explain, so the in-order form stays.
 #pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
-    const int s = c & 1;
-    const uint32_t par = (uint32_t)((c >> 1) & 1);
-    const int tok0 = (int)(x.t0 + (long long)c * C);
-    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-    if (lane == 0) {
+    {
+      const int s = c & 1;
+      const uint32_t par = (uint32_t)((c >> 1) & 1);
+      const int tok0 = (int)(x.t0 + (long long)c * C);
+      uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+      const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
       x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
       tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), FE == 1 ? 16384u : 8192u);
       tma::load_3d(smem_u32(raw + RAW_G), &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
-    } else if (lane == 1) {
-      const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
       x.wait1(B_QK_EMPTY + s, par ^ 1, E_LOAD);
       tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
       tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
       tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
       tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
       tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
-    } else {
+    }
+    {
+      const int s = c & 1;
+      const uint32_t par = (uint32_t)((c >> 1) & 1);
+      const int tok0 = (int)(x.t0 + (long long)c * C);
       const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
       x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
       tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
@@ -474,46 +487,63 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
   constexpr uint32_t ID2B = make_idesc(FMT_TF32, 128, 32, 0, 0, 1);
   constexpr uint32_t ID3A = make_idesc(FMT_TF32, 128, 128, 0, 1, 0);
   constexpr uint32_t ID3B = make_idesc(FMT_TF32, 128, 32, 0, 0, 0);
-  const uint32_t tS = tmem + TM_S, tU = tmem + TM_U;
+  const uint32_t tS = tmem + TM_S;
+  // Descriptors of stage 0, built once; a stage or K step only moves the 14-bit start-address field (units of 16
+  // bytes), so every other descriptor is one 64-bit add away.  Issuing an MMA must stay cheap: this thread issues
+  // about 30 small MMAs per chunk and is the one serial resource of the CTA.
+  const uint64_t d_kdqd = make_sdesc(sb + OFF_CONS + CS_KDQD, 16, 1024, LAYOUT_SW128);
+  const uint64_t d_v = make_sdesc(sb + OFF_CONS + CS_V, 4096, 1024, LAYOUT_SW128);
+  const uint64_t d_tbh = make_sdesc(sb + OFF_TBH, 16, 512, LAYOUT_SW64);
+  const uint64_t d_tb = make_sdesc(sb + OFF_CONS + CS_TB, 16, 1024, LAYOUT_SW128);
+  const uint64_t d_kr = make_sdesc(sb + OFF_CONS + CS_KR, 512, 2048, LAYOUT_SW128_BASE32B);
+  const uint64_t d_m = make_sdesc(sb + OFF_CONS + CS_M, 16, 1024, LAYOUT_SW128);
   x.wait1(B_S_READY, 0, E_MMA);                    // initial state is in tensor memory
 #pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
-    const uint32_t cons = sb + OFF_CONS + s * CS_STAGE;
+    const uint64_t so = (uint64_t)(s * (CS_STAGE >> 4));          // stage offset in the start-address field
+    const uint64_t so_tbh = (uint64_t)(s * (2048 >> 4));
     const uint32_t tWO = tmem + TM_WO + 64 * s;
+    const uint32_t tU = tmem + TM_U + 32 * s;             // U alternates too: MMA2 of the next chunk never overwrites
+                                                          // columns that MMA3 of this chunk may still be reading
     x.wait1(B_P1_FULL + s, par, E_MMA);
     x.wait1(B_O_EMPTY + s, par ^ 1, E_MMA);
     tc_fence_after();
+    PROF_BEGIN;
 #pragma unroll
     for (int ks = 0; ks < 16; ks++)
-      mma_ts_tf32(tWO, tS + 8 * ks, make_sdesc(cons + CS_KDQD + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, LAYOUT_SW128), ID1, ks > 0);
+      mma_ts_tf32(tWO, tS + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0);
+    // The state is handed to the scaler only when the whole of MMA1 has completed.  Releasing it 32 columns at a
+    // time (a commit after every fourth K step, each K step reading 8 state columns) was tried and produced
+    // intermittent mismatches on hardware, so the coarse hand-off stays.
     mma_commit(x.bar(B_MMA1_DONE));
     mma_commit(x.bar(B_KDQD_EMPTY + s));                  // [kd ; qd] of this stage may be rewritten
+    PROF_STAMP(4, 26);
     x.wait1(B_INV_FULL + s, par, E_MMA);
-    tc_fence_after();
     x.wait1(B_V_FULL + s, par, E_MMA);
     tc_fence_after();
     if (!v_zero) {
 #pragma unroll
       for (int ks = 0; ks < 2; ks++)
-        mma_ss_f16(tU, make_sdesc(cons + CS_V + 2 * ks * 1024, 4096, 1024, LAYOUT_SW128),
-                   make_sdesc(sb + OFF_TBH + s * 2048 + ks * 32, 16, 512, LAYOUT_SW64), ID2A, ks > 0);
+        mma_ss_f16(tU, d_v + so + (uint64_t)((2 * ks * 1024) >> 4), d_tbh + so_tbh + (uint64_t)((ks * 32) >> 4), ID2A, ks > 0);
     }
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
-      mma_ts_tf32(tU, tWO + 8 * ks, make_sdesc(cons + CS_TB + ks * 32, 16, 1024, LAYOUT_SW128), ID2B, (ks > 0) || !v_zero);
+      mma_ts_tf32(tU, tWO + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero);
+    PROF_STAMP(4, 27);
     mma_commit(x.bar(B_V_EMPTY + s));                     // the v tile may be refilled once MMA2 has read it
     x.wait1(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA);   // scaler finished St <- St diag(2^G31)
     tc_fence_after();
 #pragma unroll
-    for (int ks = 0; ks < 4; ks++)
-      mma_ts_tf32(tS, tU + 8 * ks, make_sdesc(cons + CS_KR + ks * 4096, 512, 2048, LAYOUT_SW128_BASE32B), ID3A, 1);
-#pragma unroll
-    for (int ks = 0; ks < 4; ks++)
-      mma_ts_tf32(tWO + 32, tU + 8 * ks, make_sdesc(cons + CS_M + ks * 32, 16, 1024, LAYOUT_SW128), ID3B, 1);
+    for (int ks = 0; ks < 4; ks++) {                       // two independent accumulation chains, interleaved
+      mma_ts_tf32(tS, tU + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1);
+      mma_ts_tf32(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1);
+    }
+    PROF_STAMP(4, 28);
     mma_commit(x.bar(B_O_FULL + s));
     mma_commit(x.bar(B_CONS_EMPTY + s));
+    PROF_STAMP(4, 29);
   }
   mma_commit(x.bar(B_MMA1_DONE));                  // the final state is complete
   mma_commit(x.bar(B_DRAIN));
@@ -737,7 +767,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);
   } else if (warp == W_LOAD) {
-    role_loader<FE>(p, maps, x, lane);
+    if (lane == 0) role_loader<FE>(p, maps, x);
     __syncwarp();
   } else if (warp < W_EPI0) {
     role_scaler<KF>(p, task, x, tmem, warp & 3, lane);
@@ -751,8 +781,8 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
 #ifdef KDA_PROF
   if (lane == 0 && blockIdx.x == 0) {
     const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_EPI0 ? 5 : (warp < W_PREP0 ? 6 : 2))));
-    atomicAdd(x.prof + role * 32 + 24, (unsigned long long)(clock64() - prof_t0));
-    atomicAdd(x.prof + role * 32 + 25, 1ull);
+    atomicAdd(x.prof + role * 64 + 62, (unsigned long long)(clock64() - prof_t0));
+    atomicAdd(x.prof + role * 64 + 63, 1ull);
   }
 #endif
   tc_fence_before();

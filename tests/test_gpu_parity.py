@@ -97,6 +97,26 @@ def test_deterministic(kda):
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_repeated_runs_are_bit_identical(kda, kernel):
+    """Many CTAs with different run lengths, several launches: any hand-off race between the warp roles shows up as a
+    run-to-run difference."""
+    lens = [256, 512, 900, 100, 160, 240, 400, 87, 1300, 33]
+    inputs = ko.make_inputs_raw(12, lens, 603)
+    gold_o, gold_s, _ = gold_raw(inputs, lens)
+    d = to_dev(inputs)
+    first = None
+    for rep in range(6):
+        out, fin = kda.prepare(*d, kernel=kernel)()
+        torch.cuda.synchronize()
+        if first is None:
+            first = (out.clone(), fin.clone())
+            ko.check_close(out.cpu(), gold_o, "repeat output")
+            ko.check_close(fin.cpu(), gold_s, "repeat final_state")
+        else:
+            assert torch.equal(out, first[0]) and torch.equal(fin, first[1]), f"run {rep} differs from run 0"
+
+
 def test_strided_head_slice_is_read_in_place(kda):
     """A head slice of wider tensors (the head-parallel layout) gives the same bits as a contiguous copy."""
     H, Hs, lens = 8, 4, [200, 77]
