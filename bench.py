@@ -41,7 +41,7 @@ BYTES_PER_TOKEN_HEAD = 3 * D * 2 + D * 4 + 4 + D * 2         # q,k,v bf16 + g fp
 METRIC = "KDA prefill tokens/s (H=64,K=V=128 varlen)"
 # dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_fwd_kernel per token-head, from the ncu capture of
 # `bench.py --small` summarised under profiles/ (traffic grows in proportion to token-heads); None until captured.
-NCU_DRAM_BYTES_PER_TOKEN_HEAD = None
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1688.3   # profiles/kda_chunk_umma_serving.md, section 2
 
 
 def workload_lengths(seed=2):
@@ -291,12 +291,16 @@ def main(argv=None):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         launch()
     barrier()
     if kda_b200.status_bits(launch) != 0 or kda_b200.kernel_error(launch) != 0:
         raise SystemExit("bench: the launch reported a table or kernel error")
-    sampler = ClockSampler(local) if rank == 0 else None
+    t_load = time.perf_counter()
+    while rank == 0 and time.perf_counter() - t_load < 0.6:     # keep the GPU busy until nvidia-smi has sampled
+        launch()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -358,7 +362,7 @@ def main(argv=None):
                        "l2": "inputs (GBs per step) far exceed L2; no flush needed", "parallelism": f"hp{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],
-                         "kernel": "kda_chunk_fwd_kernel (the step also holds the planner kernel, < 1 % of the time)",
+                         "kernel": "kda_chunk_umma_kernel (the step also holds kda_plan_kernel, 0.65 % of the time)",
                          "algorithmic_bytes_per_launch": algo_bytes},
             "tensor": {"achieved": tf, "peak": pk["tf"], "unit": "TFLOP/s", "frac": tf / pk["tf"],
                        "flops_per_launch": flops, "note": "dense count 163840 FLOP per token-head (chunk 64 convention)"},
