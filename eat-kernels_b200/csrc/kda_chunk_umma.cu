@@ -16,8 +16,9 @@
 // than a bf16 copy would.
 //
 // Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-7 scaler (state load / decay /
-// checkpoints / final store), 8-11 epilogue (O -> bf16 -> global), 12-27 operand preparation in two groups of eight
+// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-11 tensor-memory
+// warps (state load / per-chunk decay / checkpoints / final store, and O -> bf16 -> global; each warp serves half of
+// the columns of one lane quarter), 12-27 operand preparation in two groups of eight
 // warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
 // (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
 // code in status[2].
@@ -580,22 +581,30 @@ __device__ __forceinline__ void store_row_piece<__nv_bfloat16>(__nv_bfloat16* ds
   }
 }
 
+// Eight warps own the tensor-memory traffic that goes through registers: warp (quarter q, half hf) serves the 32
+// value rows [32 q, 32 q + 32) (the tensor-memory lanes a warp with id % 4 == q may touch) and, of those, the state
+// columns [64 hf, 64 hf + 64) and the output tokens [16 hf, 16 hf + 16) of every chunk.  Per chunk:
+//   wait MMA1 done -> (checkpoint row if due) -> St <- St diag(2^G31) for its columns -> signal S_READY        (on the chain)
+//   wait MMA3 done -> O columns -> registers -> release the O buffer -> bf16 -> global                         (off the chain)
+// plus the initial state load and the final state store for its columns.
 template <int KF>
-__device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
+__device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int hf, int lane) {
   const int v = 32 * quarter + lane;
-  const uint32_t tS = tmem + TM_S + ((uint32_t)(32 * quarter) << 16);
+  const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+  const uint32_t tS = tmem + TM_S + lane_base + 64 * hf;
   // ---- initial state -> tensor memory
 #pragma unroll 1
-  for (int j = 0; j < 4; j++) {
+  for (int j = 0; j < 2; j++) {
+    const int col0 = 64 * hf + 32 * j;
     uint32_t r[32];
     if (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY)) {
       const float one = (task.flags & TF_INIT_IDENTITY) ? 1.0f : 0.0f;
 #pragma unroll
-      for (int i = 0; i < 32; i++) r[i] = __float_as_uint((32 * j + i == v) ? one : 0.0f);
+      for (int i = 0; i < 32; i++) r[i] = __float_as_uint((col0 + i == v) ? one : 0.0f);
     } else {
       const float* src = task.src + (size_t)x.h * STATE_ELEMS;
       if (!KF) {
-        const float4* s4 = reinterpret_cast<const float4*>(src + v * D + 32 * j);
+        const float4* s4 = reinterpret_cast<const float4*>(src + v * D + col0);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const float4 f = s4[i];
@@ -603,7 +612,7 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(src[(32 * j + i) * D + v]);
+        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(src[(col0 + i) * D + v]);
       }
     }
     tmem_st32(tS + 32 * j, r);
@@ -613,6 +622,7 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
   __syncwarp();
   if (lane == 0) mbar_arrive(x.bar(B_S_READY));
 
+  __nv_bfloat16* obase = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
 #pragma unroll 1
   for (int c = 0; c <= x.nchunks; c++) {
     x.wait(B_MMA1_DONE, (uint32_t)(c & 1), E_SCALE);
@@ -623,20 +633,21 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
     long long ck_off = 0;
     if (ck) ck_off = (long long)(c / p.ck_every_chunks) * p.ck_row_stride + (long long)x.h * STATE_ELEMS;
 #pragma unroll 1
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 2; j++) {
+      const int col0 = 64 * hf + 32 * j;
       uint32_t r[32];
       tmem_ld32(tS + 32 * j, r);
       tmem_wait_ld();
       if (ck) {
-        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, KF, v, 32 * j, r);
-        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, KF, v, 32 * j, r);
+        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, KF, v, col0, r);
+        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, KF, v, col0, r);
       }
       if (last) {
-        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, KF, v, 32 * j, r);
+        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, KF, v, col0, r);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dec + 32 * j + 4 * i);
+          const float4 d4 = *reinterpret_cast<const float4*>(dec + col0 + 4 * i);
           const float2 lo = mul2(make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), make_float2(d4.x, d4.y));
           const float2 hi = mul2(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), make_float2(d4.z, d4.w));
           r[4 * i] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
@@ -645,36 +656,28 @@ __device__ void role_scaler(const ChunkParams& p, const Task& task, const Ctx& x
         tmem_st32(tS + 32 * j, r);
       }
     }
-    if (!last) {
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(x.bar(B_S_READY));
-    }
-  }
-}
+    if (last) break;
+    tmem_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(x.bar(B_S_READY));
 
-// ------------------------------------------------------------------------------------------------ epilogue warps
-__device__ void role_epilogue(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int lane) {
-  const int v = 32 * quarter + lane;
-  __nv_bfloat16* obase = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
-#pragma unroll 1
-  for (int c = 0; c < x.nchunks; c++) {
+    // ---- output rows of this chunk
     const int s = c & 1;
-    x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI, 256);   // off the critical chain: poll rarely
+    x.wait(B_O_FULL + s, (uint32_t)((c >> 1) & 1), E_EPI);
     tc_fence_after();
-    uint32_t r[32];
-    tmem_ld32(tmem + TM_WO + 64 * s + 32 + ((uint32_t)(32 * quarter) << 16), r);
+    uint32_t o[16];
+    tmem_ld16(tmem + TM_WO + 64 * s + 32 + 16 * hf + lane_base, o);
     tmem_wait_ld();
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + s));
     if (!(task.flags & TF_NO_OUT)) {
       const int nvalid = min(C, x.len - c * C);
-      __nv_bfloat16* o = obase + (x.t0 + (long long)c * C) * p.ldo;
+      __nv_bfloat16* orow = obase + (x.t0 + (long long)c * C + 16 * hf) * p.ldo;
 #pragma unroll
-      for (int i = 0; i < C; i++)
-        if (i < nvalid) o[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(r[i]));
+      for (int i = 0; i < 16; i++)
+        if (16 * hf + i < nvalid) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
     }
   }
 }
@@ -744,10 +747,10 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
       mbar_init(x.bar(B_V_EMPTY + i), 1);
       mbar_init(x.bar(B_L_EMPTY + i), 1);
       mbar_init(x.bar(B_O_FULL + i), 1);
-      mbar_init(x.bar(B_O_EMPTY + i), 4);
+      mbar_init(x.bar(B_O_EMPTY + i), 8);
     }
     mbar_init(x.bar(B_MMA1_DONE), 1);
-    mbar_init(x.bar(B_S_READY), 4);
+    mbar_init(x.bar(B_S_READY), 8);
     mbar_init(x.bar(B_DRAIN), 1);
     fence_barrier_init();
   }
@@ -769,10 +772,8 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   } else if (warp == W_LOAD) {
     if (lane == 0) role_loader<FE>(p, maps, x);
     __syncwarp();
-  } else if (warp < W_EPI0) {
-    role_scaler<KF>(p, task, x, tmem, warp & 3, lane);
   } else if (warp < W_PREP0) {
-    role_epilogue(p, task, x, tmem, warp & 3, lane);
+    role_tmem<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
   } else {
     const int pt = tid - W_PREP0 * 32;
     role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
