@@ -16,7 +16,7 @@
 // than a bf16 copy would.
 //
 // Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (one lane drives the TMA copies of the raw tiles; v goes straight into the consumer stage), 4-11 tensor-memory
+// 3 loader (two lanes drive the TMA copy streams g + q,k and v; v goes straight into the consumer stage), 4-11 tensor-memory
 // warps (state load / per-chunk decay / checkpoints / final store, and O -> bf16 -> global; each warp serves half of
 // the columns of one lane quarter), 12-27 operand preparation in two groups of eight
 // warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
@@ -123,20 +123,19 @@ struct Ctx {
 // tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
 // MN-major 128-byte-swizzled layout is exactly what the engine writes), plus L2 prefetches two chunks ahead.
 template <int FE>
-__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x) {   // one thread
-  // One thread requests every tile of chunk c in the order the buffers come free: the gate tile (free after step B
-  // of chunk c-2), q / k (free after step C), v (free once MMA2 of chunk c-2 has read it).  Each tile has its own
-  // full / empty barrier pair, so consumers start on a tile as soon as it has landed.
-  // Requesting the tiles of later chunks without waiting for the v buffer (separate lanes per stream, or v deferred by
-  // one chunk) was tried: it let the preparation run further ahead of the tensor core and produced intermittent
-  // mismatches on hardware that reading the hand-offs did not explain, so the in-order form stays.
+__device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
+  // Two independent copy streams, one lane each, so that the late release of the v buffer (free only once MMA2 of
+  // the chunk two back has read it) never delays the refill of the gate and q / k tiles: lane 0 requests g (buffer
+  // free after step B of the chunk two back) and then q / k (free after step C); lane 1 requests v.  Every tile has
+  // its own full / empty barrier pair, and every consumer of a barrier observes each of its phases.
+  if (lane > 1) return;
 #pragma unroll 1
   for (int c = 0; c < x.nchunks; c++) {
-    {
-      const int s = c & 1;
-      const uint32_t par = (uint32_t)((c >> 1) & 1);
-      const int tok0 = (int)(x.t0 + (long long)c * C);
-      uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1);
+    const int tok0 = (int)(x.t0 + (long long)c * C);
+    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+    if (lane == 0) {
       const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
       x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
       tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), FE == 1 ? 16384u : 8192u);
@@ -147,11 +146,7 @@ __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x
       tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
       tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
       tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
-    }
-    {
-      const int s = c & 1;
-      const uint32_t par = (uint32_t)((c >> 1) & 1);
-      const int tok0 = (int)(x.t0 + (long long)c * C);
+    } else {
       const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
       x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
       tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
@@ -198,19 +193,6 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     float* dec = reinterpret_cast<float*>(x.smem + OFF_DEC) + (c & 3) * D;
     x.wait(B_G_FULL + s, par, E_PREP);
     PROF_BEGIN;
-    if (nvalid < C) {
-      x.wait(B_V_FULL + s, par, E_PREP);
-      // last, partial chunk: the v rows past the end of the run hold another sequence's data (or worse): zero them so
-      // that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  Whole 128-byte lines.
-      for (int i = ptid; i < (C - nvalid) * 16; i += PREP_THREADS) {
-        const int row = nvalid + (i >> 4), piece = i & 15;
-        *reinterpret_cast<uint4*>(cons + CS_V + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-    if (ptid < C) {
-      beta_s[ptid] = beta_next;                        // read after the barriers of step A
-      if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
-    }
 
     // ---- A: gate activation + inclusive cumulative log2-decay; two threads per channel, 16 tokens each.
     // Touches only prep-private scratch (the decay slot c & 3 was last read four chunks ago), so it runs while the
@@ -234,6 +216,11 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
       }
       if (half == 0) tot[ch] = a[15];
       named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
+      // Every warp of the group has left the previous chunk (step C reads beta_s), so beta may be replaced only now.
+      if (ptid < C) {
+        beta_s[ptid] = beta_next;
+        if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
+      }
       if (half == 1) {
         const float r = tot[ch];
 #pragma unroll
@@ -462,6 +449,21 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
     __syncwarp();
     const float bc = reinterpret_cast<const float*>(x.smem + OFF_LBETA)[s * 32 + lane];
     PROF_STAMP(3, 26);
+    // The v tile of a partial last chunk holds another sequence's rows (or worse) past the end of the run: zero them
+    // so that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  This warp observes every
+    // phase of the v barrier of its stage, so the wait cannot be satisfied by an older phase, and MMA2 waits for this
+    // warp's INV_FULL arrival.
+    x.wait(B_V_FULL + s, par, E_INV);
+    {
+      const int nvalid = min(C, x.len - c * C);
+      if (nvalid < C) {
+        uint8_t* vt = x.smem + OFF_CONS + s * CS_STAGE + CS_V;
+        for (int i = lane; i < (C - nvalid) * 16; i += 32) {     // whole 128-byte lines of both 64-channel halves
+          const int row = nvalid + (i >> 4), piece = i & 15;
+          *reinterpret_cast<uint4*>(vt + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
     x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
     uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
     uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
@@ -515,10 +517,7 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
 #pragma unroll
     for (int ks = 0; ks < 16; ks++)
       mma_ts_tf32(tWO, tS + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0);
-    // The state is handed to the scaler only when the whole of MMA1 has completed.  Releasing it 32 columns at a
-    // time (a commit after every fourth K step, each K step reading 8 state columns) was tried and produced
-    // intermittent mismatches on hardware, so the coarse hand-off stays.
-    mma_commit(x.bar(B_MMA1_DONE));
+    mma_commit(x.bar(B_MMA1_DONE));                       // the tensor-memory warps may rescale the state
     mma_commit(x.bar(B_KDQD_EMPTY + s));                  // [kd ; qd] of this stage may be rewritten
     PROF_STAMP(4, 26);
     x.wait1(B_INV_FULL + s, par, E_MMA);
@@ -770,7 +769,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);
   } else if (warp == W_LOAD) {
-    if (lane == 0) role_loader<FE>(p, maps, x);
+    role_loader<FE>(p, maps, x, lane);
     __syncwarp();
   } else if (warp < W_PREP0) {
     role_tmem<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
@@ -781,7 +780,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
 
 #ifdef KDA_PROF
   if (lane == 0 && blockIdx.x == 0) {
-    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_EPI0 ? 5 : (warp < W_PREP0 ? 6 : 2))));
+    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_PREP0 ? 5 : 2)));
     atomicAdd(x.prof + role * 64 + 62, (unsigned long long)(clock64() - prof_t0));
     atomicAdd(x.prof + role * 64 + 63, 1ull);
   }
