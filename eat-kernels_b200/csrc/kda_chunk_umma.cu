@@ -483,7 +483,14 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
 }
 
 // ------------------------------------------------------------------------------------------------ MMA issuer
-__device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
+// Runs on ALL lanes of warp 0 with warp-uniform values only; one elected lane issues the tensor-core instructions
+// (predicated inside the asm).  Keeping the control flow convergent lets the compiler hold descriptors, tensor-memory
+// addresses and barrier addresses in uniform registers, which is what makes issuing ~34 small MMAs per chunk cheap.
+__device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
+  const uint32_t go = elect_one();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_any, 0);
+  const bool v_zero = __shfl_sync(0xffffffffu, (int)v_zero_any, 0) != 0;
+  const int nchunks = __shfl_sync(0xffffffffu, x.nchunks, 0);
   const uint32_t sb = smem_u32(x.smem);
   constexpr uint32_t ID1 = make_idesc(FMT_TF32, 128, 64, 0, 0, 0);
   constexpr uint32_t ID2A = make_idesc(FMT_BF16, 128, 32, 1, 0, 0);
@@ -492,17 +499,16 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
   constexpr uint32_t ID3B = make_idesc(FMT_TF32, 128, 32, 0, 0, 0);
   const uint32_t tS = tmem + TM_S;
   // Descriptors of stage 0, built once; a stage or K step only moves the 14-bit start-address field (units of 16
-  // bytes), so every other descriptor is one 64-bit add away.  Issuing an MMA must stay cheap: this thread issues
-  // about 30 small MMAs per chunk and is the one serial resource of the CTA.
+  // bytes), so every other descriptor is one 64-bit add away.
   const uint64_t d_kdqd = make_sdesc(sb + OFF_CONS + CS_KDQD, 16, 1024, LAYOUT_SW128);
   const uint64_t d_v = make_sdesc(sb + OFF_CONS + CS_V, 4096, 1024, LAYOUT_SW128);
   const uint64_t d_tbh = make_sdesc(sb + OFF_TBH, 16, 512, LAYOUT_SW64);
   const uint64_t d_tb = make_sdesc(sb + OFF_CONS + CS_TB, 16, 1024, LAYOUT_SW128);
   const uint64_t d_kr = make_sdesc(sb + OFF_CONS + CS_KR, 512, 2048, LAYOUT_SW128_BASE32B);
   const uint64_t d_m = make_sdesc(sb + OFF_CONS + CS_M, 16, 1024, LAYOUT_SW128);
-  x.wait1(B_S_READY, 0, E_MMA);                    // initial state is in tensor memory
+  x.wait(B_S_READY, 0, E_MMA, 0);                  // initial state is in tensor memory
 #pragma unroll 1
-  for (int c = 0; c < x.nchunks; c++) {
+  for (int c = 0; c < nchunks; c++) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
     const uint64_t so = (uint64_t)(s * (CS_STAGE >> 4));          // stage offset in the start-address field
@@ -510,44 +516,44 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem, bool v_zero) {
     const uint32_t tWO = tmem + TM_WO + 64 * s;
     const uint32_t tU = tmem + TM_U + 32 * s;             // U alternates too: MMA2 of the next chunk never overwrites
                                                           // columns that MMA3 of this chunk may still be reading
-    x.wait1(B_P1_FULL + s, par, E_MMA);
-    x.wait1(B_O_EMPTY + s, par ^ 1, E_MMA);
+    x.wait(B_P1_FULL + s, par, E_MMA, 0);
+    x.wait(B_O_EMPTY + s, par ^ 1, E_MMA, 0);
     tc_fence_after();
     PROF_BEGIN;
 #pragma unroll
     for (int ks = 0; ks < 16; ks++)
-      mma_ts_tf32(tWO, tS + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0);
-    mma_commit(x.bar(B_MMA1_DONE));                       // the tensor-memory warps may rescale the state
-    mma_commit(x.bar(B_KDQD_EMPTY + s));                  // [kd ; qd] of this stage may be rewritten
+      mma_ts_tf32_pred(tWO, tS + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
+    mma_commit_pred(x.bar(B_MMA1_DONE), go);              // the tensor-memory warps may rescale the state
+    mma_commit_pred(x.bar(B_KDQD_EMPTY + s), go);         // [kd ; qd] of this stage may be rewritten
     PROF_STAMP(4, 26);
-    x.wait1(B_INV_FULL + s, par, E_MMA);
-    x.wait1(B_V_FULL + s, par, E_MMA);
+    x.wait(B_INV_FULL + s, par, E_MMA, 0);
+    x.wait(B_V_FULL + s, par, E_MMA, 0);
     tc_fence_after();
     if (!v_zero) {
 #pragma unroll
       for (int ks = 0; ks < 2; ks++)
-        mma_ss_f16(tU, d_v + so + (uint64_t)((2 * ks * 1024) >> 4), d_tbh + so_tbh + (uint64_t)((ks * 32) >> 4), ID2A, ks > 0);
+        mma_ss_f16_pred(tU, d_v + so + (uint64_t)((2 * ks * 1024) >> 4), d_tbh + so_tbh + (uint64_t)((ks * 32) >> 4), ID2A, ks > 0, go);
     }
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
-      mma_ts_tf32(tU, tWO + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero);
+      mma_ts_tf32_pred(tU, tWO + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero, go);
     PROF_STAMP(4, 27);
-    mma_commit(x.bar(B_V_EMPTY + s));                     // the v tile may be refilled once MMA2 has read it
-    x.wait1(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA);   // scaler finished St <- St diag(2^G31)
+    mma_commit_pred(x.bar(B_V_EMPTY + s), go);            // the v tile may be refilled once MMA2 has read it
+    x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0); // scaler finished St <- St diag(2^G31)
     tc_fence_after();
 #pragma unroll
     for (int ks = 0; ks < 4; ks++) {                       // two independent accumulation chains, interleaved
-      mma_ts_tf32(tS, tU + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1);
-      mma_ts_tf32(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1);
+      mma_ts_tf32_pred(tS, tU + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
+      mma_ts_tf32_pred(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
     }
     PROF_STAMP(4, 28);
-    mma_commit(x.bar(B_O_FULL + s));
-    mma_commit(x.bar(B_CONS_EMPTY + s));
+    mma_commit_pred(x.bar(B_O_FULL + s), go);
+    mma_commit_pred(x.bar(B_CONS_EMPTY + s), go);
     PROF_STAMP(4, 29);
   }
-  mma_commit(x.bar(B_MMA1_DONE));                  // the final state is complete
-  mma_commit(x.bar(B_DRAIN));
-  x.wait1(B_DRAIN, 0, E_MMA);
+  mma_commit_pred(x.bar(B_MMA1_DONE), go);         // the final state is complete
+  mma_commit_pred(x.bar(B_DRAIN), go);
+  x.wait(B_DRAIN, 0, E_MMA, 0);
 }
 
 // ------------------------------------------------------------------------------------------------ scaler warps
@@ -685,7 +691,8 @@ __device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, 
 template <int FE, int KF>
 __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = tid >> 5;
   const int H = p.H;
   const int rank = blockIdx.x / H, h = blockIdx.x % H;
 
@@ -764,7 +771,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   const bool v_zero = (task.flags & TF_V_ZERO) != 0;
 
   if (warp == W_MMA) {
-    if (lane == 0) role_mma(x, tmem, v_zero);
+    role_mma(x, tmem, v_zero);
     __syncwarp();
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);

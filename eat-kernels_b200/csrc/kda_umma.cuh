@@ -168,6 +168,32 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(bar) : "memory");
 }
 
+// Warp-convergent issue.  The tensor-core instructions take their descriptors and addresses from warp-uniform
+// registers.  When the issuing code sits inside a one-lane branch the compiler has to move every operand from a
+// vector register into a uniform one right before each instruction, which serialises at roughly 50 cycles per
+// MMA; when the WHOLE warp runs the issuing code with warp-uniform operands and only the instruction itself is
+// predicated on the elected lane, the operands are computed in uniform registers and an MMA issues in under 20
+// cycles.  `go` is the result of elect_one() taken once: the same lane must issue the MMAs and their commits.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void mma_ss_f16_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint32_t go) {
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %5, 0;\n"
+               " @q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go) : "memory");
+}
+__device__ __forceinline__ void mma_ts_tf32_pred(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint32_t go) {
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %5, 0;\n"
+               " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
+               :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go) : "memory");
+}
+__device__ __forceinline__ void mma_commit_pred(uint32_t bar, uint32_t go) {
+  asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n"
+               " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" :: "r"(bar), "r"(go) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------- tile addressing
 // K-major SW128 tile of 32-bit elements, rows of 128 bytes (32 elements), K blocks `kblock_bytes` apart:
 // byte offset of element (row, k).
