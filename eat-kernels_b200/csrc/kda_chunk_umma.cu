@@ -215,7 +215,9 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         if (i > 0) a[i] += a[i - 1];
       }
       if (half == 0) tot[ch] = a[15];
+      PROF_STAMP(2, 10);
       named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
+      PROF_STAMP(2, 11);
       // Every warp of the group has left the previous chunk (step C reads beta_s), so beta may be replaced only now.
       if (ptid < C) {
         beta_s[ptid] = beta_next;
@@ -233,6 +235,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
 #pragma unroll
       for (int i = 0; i < 16; i++) Gsm[(16 * half + i) * D + ch] = a[i];
     }
+    PROF_STAMP(2, 12);
     named_bar_sync(bar_id, PREP_THREADS);
     PROF_STAMP(2, 26);
 
@@ -240,6 +243,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     // soon as MMA1 of the chunk two back has read the stage; kr waits in registers until MMA3 has released the rest.
     x.wait(B_QK_FULL + s, par, E_PREP);
     x.wait(B_KDQD_EMPTY + s, par ^ 1, E_PREP);
+    PROF_STAMP(2, 14);
     float krr[4][4];
     {
       const float4 r4 = *reinterpret_cast<const float4*>(fr + 4 * lane);
@@ -325,6 +329,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
           mma_bf16(acc[1], a, b[2], b[3]);
         }
       }
+      PROF_STAMP(2, 15);
       if (which == 0) {
         x.wait(B_L_EMPTY + s, par ^ 1, E_PREP);
         float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
@@ -339,8 +344,10 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         __syncwarp();
         if (lane == 0) mbar_arrive(x.bar(B_L_FULL + s));      // the inverse of this chunk may start
       }
+      PROF_STAMP(2, 16);
       // ---- D: the operands of MMA3 go out once the tensor core has released the rest of the stage
       x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
+      PROF_STAMP(2, 17);
 #pragma unroll
       for (int tt = 0; tt < 4; tt++)
         *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, 4 * pw + tt, 512, 2048)) =
@@ -447,7 +454,7 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
       }
     }
     __syncwarp();
-    const float bc = reinterpret_cast<const float*>(x.smem + OFF_LBETA)[s * 32 + lane];
+    const float* lbeta = reinterpret_cast<const float*>(x.smem + OFF_LBETA) + s * 32;
     PROF_STAMP(3, 26);
     // The v tile of a partial last chunk holds another sequence's rows (or worse) past the end of the run: zero them
     // so that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  This warp observes every
@@ -467,11 +474,21 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
     x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
     uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
     uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
-#pragma unroll 4
-    for (int i = 0; i < C; i++) {
-      const float val = Lsm[i * C + lane] * bc;
-      *reinterpret_cast<float*>(tb + kmajor_f32_off(i, lane, 0)) = val;
-      *reinterpret_cast<__nv_bfloat16*>(tbh + kmajor_b16_sw64_off(i, lane)) = __float2bfloat16_rn(val);
+    // Tb = T diag(beta): lane = row; eight columns (one 16-byte bf16 chunk, two 16-byte tf32 chunks) per step, the
+    // column group rotated by the lane so that the wide loads and stores of a quarter-warp spread over the banks.
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+      const int c0 = 8 * ((jj + lane) & 3);
+      const float4 ta = *reinterpret_cast<const float4*>(Lsm + lane * C + c0);
+      const float4 tc = *reinterpret_cast<const float4*>(Lsm + lane * C + c0 + 4);
+      const float4 ba = *reinterpret_cast<const float4*>(lbeta + c0);
+      const float4 bb = *reinterpret_cast<const float4*>(lbeta + c0 + 4);
+      const float4 va = make_float4(ta.x * ba.x, ta.y * ba.y, ta.z * ba.z, ta.w * ba.w);
+      const float4 vb = make_float4(tc.x * bb.x, tc.y * bb.y, tc.z * bb.z, tc.w * bb.w);
+      *reinterpret_cast<float4*>(tb + kmajor_f32_off(lane, c0, 0)) = va;
+      *reinterpret_cast<float4*>(tb + kmajor_f32_off(lane, c0 + 4, 0)) = vb;
+      *reinterpret_cast<uint4*>(tbh + kmajor_b16_sw64_off(lane, c0)) =
+          make_uint4(pack_bf16(va.x, va.y), pack_bf16(va.z, va.w), pack_bf16(vb.x, vb.y), pack_bf16(vb.z, vb.w));
     }
     fence_proxy_async();
     __syncwarp();
