@@ -16,7 +16,7 @@
 // than a bf16 copy would.
 //
 // Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (two lanes drive the TMA copy streams g + q,k and v; v goes straight into the consumer stage), 4-11 tensor-memory
+// 3 loader (one lane polls three TMA copy streams g / q,k / v; v goes straight into the consumer stage), 4-11 tensor-memory
 // warps (state load / per-chunk decay / checkpoints / final store, and O -> bf16 -> global; each warp serves half of
 // the columns of one lane quarter), 12-27 operand preparation in two groups of eight
 // warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
@@ -121,37 +121,75 @@ struct Ctx {
 // ------------------------------------------------------------------------------------------------ loader warp
 // One elected lane drives the copy engine: per chunk it arms the stage's mbarrier with the byte count and issues the
 // tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
-// MN-major 128-byte-swizzled layout is exactly what the engine writes), plus L2 prefetches two chunks ahead.
+// MN-major 128-byte-swizzled layout is exactly what the engine writes).
 template <int FE>
 __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
-  // Two independent copy streams, one lane each, so that the late release of the v buffer (free only once MMA2 of
-  // the chunk two back has read it) never delays the refill of the gate and q / k tiles: lane 0 requests g (buffer
-  // free after step B of the chunk two back) and then q / k (free after step C); lane 1 requests v.  Every tile has
-  // its own full / empty barrier pair, and every consumer of a barrier observes each of its phases.
-  if (lane > 1) return;
+  // Three independent copy streams (g; q and k; v), each with its own full / empty barrier pair per stage: the gate
+  // tile is free after step B of the chunk two back, q / k after step C, v only once MMA2 has read it.  ONE lane
+  // serves all three by polling the empty barriers without blocking: a blocking wait of one stream (or of a second
+  // lane of this warp, which shares the warp's single scheduling slot) would delay the refill of the others by its
+  // suspend time, and the refill latency of q / k sits on the chain  copy -> step B -> step C -> inverse -> MMA2.
+  if (lane != 0) return;
+  const int n = x.nchunks;
+  int cg = 0, cq = 0, cv = 0;                 // next chunk of each stream
+  unsigned idle = 0;
+  unsigned long long t_idle = 0;
 #pragma unroll 1
-  for (int c = 0; c < x.nchunks; c++) {
-    const int s = c & 1;
-    const uint32_t par = (uint32_t)((c >> 1) & 1);
-    const int tok0 = (int)(x.t0 + (long long)c * C);
-    uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-    if (lane == 0) {
-      const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
-      x.wait1(B_G_EMPTY + s, par ^ 1, E_LOAD);
-      tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), FE == 1 ? 16384u : 8192u);
-      tma::load_3d(smem_u32(raw + RAW_G), &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
-      x.wait1(B_QK_EMPTY + s, par ^ 1, E_LOAD);
-      tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
-      tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-      tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
-      tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-      tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+  while (cg < n || cq < n || cv < n) {
+    bool progressed = false;
+    if (cq < n) {
+      const int s = cq & 1;
+      if (mbar_test_wait(x.bar(B_QK_EMPTY + s), (uint32_t)(((cq >> 1) & 1) ^ 1))) {
+        uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+        const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
+        const int tok0 = (int)(x.t0 + (long long)cq * C);
+        tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
+        tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+        tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+        tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
+        tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+        cq++;
+        progressed = true;
+      }
+    }
+    if (cg < n) {
+      const int s = cg & 1;
+      if (mbar_test_wait(x.bar(B_G_EMPTY + s), (uint32_t)(((cg >> 1) & 1) ^ 1))) {
+        uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
+        const int tok0 = (int)(x.t0 + (long long)cg * C);
+        tma::mbar_arrive_expect_tx(x.bar(B_G_FULL + s), FE == 1 ? 16384u : 8192u);
+        tma::load_3d(smem_u32(raw + RAW_G), &m.g, 0, x.h, tok0, x.bar(B_G_FULL + s));
+        cg++;
+        progressed = true;
+      }
+    }
+    if (cv < n) {
+      const int s = cv & 1;
+      if (mbar_test_wait(x.bar(B_V_EMPTY + s), (uint32_t)(((cv >> 1) & 1) ^ 1))) {
+        const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
+        const int tok0 = (int)(x.t0 + (long long)cv * C);
+        tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
+        tma::load_3d(vdst, &m.v, 0, x.h, tok0, x.bar(B_V_FULL + s));
+        tma::load_3d(vdst + 4096, &m.v, 64, x.h, tok0, x.bar(B_V_FULL + s));
+        cv++;
+        progressed = true;
+      }
+    }
+    if (progressed) {
+      idle = 0;
+      t_idle = 0;
     } else {
-      const uint32_t vdst = smem_u32(x.smem + OFF_CONS + s * CS_STAGE + CS_V);
-      x.wait1(B_V_EMPTY + s, par ^ 1, E_LOAD);
-      tma::mbar_arrive_expect_tx(x.bar(B_V_FULL + s), 8192u);
-      tma::load_3d(vdst, &m.v, 0, x.h, tok0, x.bar(B_V_FULL + s));
-      tma::load_3d(vdst + 4096, &m.v, 64, x.h, tok0, x.bar(B_V_FULL + s));
+      // nothing to refill yet: back off briefly; give up like every other wait of the kernel does
+      __nanosleep(32);
+      if (*x.abort_flag != 0) break;
+      if ((++idle & 1023u) == 0) {
+        const unsigned long long now = global_timer_ns();
+        if (t_idle == 0) t_idle = now;
+        else if (now - t_idle > kWaitLimitNs) {
+          atomicCAS(const_cast<int*>(x.abort_flag), 0, E_LOAD);
+          break;
+        }
+      }
     }
   }
 }
