@@ -594,15 +594,16 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
       mma_ts_tf32_pred(tU, tWO + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero, go);
     PROF_STAMP(4, 27);
     mma_commit_pred(x.bar(B_V_EMPTY + s), go);            // the v tile may be refilled once MMA2 has read it
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)                        // O += U M^T does not touch the state: issued before the wait
+      mma_ts_tf32_pred(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
+    mma_commit_pred(x.bar(B_O_FULL + s), go);
     x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0); // scaler finished St <- St diag(2^G31)
     tc_fence_after();
 #pragma unroll
-    for (int ks = 0; ks < 4; ks++) {                       // two independent accumulation chains, interleaved
+    for (int ks = 0; ks < 4; ks++)
       mma_ts_tf32_pred(tS, tU + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
-      mma_ts_tf32_pred(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
-    }
     PROF_STAMP(4, 28);
-    mma_commit_pred(x.bar(B_O_FULL + s), go);
     mma_commit_pred(x.bar(B_CONS_EMPTY + s), go);
     PROF_STAMP(4, 29);
   }
@@ -638,6 +639,36 @@ __device__ __forceinline__ void store_row_piece<__nv_bfloat16>(__nv_bfloat16* ds
   } else {
 #pragma unroll
     for (int i = 0; i < 32; i++) dst[(col0 + i) * D + v] = __float2bfloat16_rn(__uint_as_float(r[i]));
+  }
+}
+
+// State columns [64 hf, 64 hf + 64) of this warp's 32 value rows: tensor memory -> final-state tensor and / or
+// checkpoint row (either may be null).
+template <int KF>
+__device__ __noinline__ void store_state_rows(uint32_t tS, float* dst, void* ck, int ck_is_bf16, int v, int hf) {
+#pragma unroll 1
+  for (int j = 0; j < 2; j++) {
+    const int col0 = 64 * hf + 32 * j;
+    uint32_t r[32];
+    tmem_ld32(tS + 32 * j, r);
+    tmem_wait_ld();
+    if (ck != nullptr) {
+      if (ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(ck), KF, v, col0, r);
+      else store_row_piece<float>(reinterpret_cast<float*>(ck), KF, v, col0, r);
+    }
+    if (dst != nullptr) store_row_piece<float>(dst, KF, v, col0, r);
+  }
+}
+
+// r[i] <- r[i] * d[i] for 16 consecutive state columns (d in shared memory, 16-byte aligned)
+__device__ __forceinline__ void scale16(uint32_t (&r)[16], const float* d) {
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float4 d4 = *reinterpret_cast<const float4*>(d + 4 * i);
+    const float2 lo = mul2(make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), make_float2(d4.x, d4.y));
+    const float2 hi = mul2(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), make_float2(d4.z, d4.w));
+    r[4 * i] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
+    r[4 * i + 2] = __float_as_uint(hi.x); r[4 * i + 3] = __float_as_uint(hi.y);
   }
 }
 
@@ -692,31 +723,36 @@ __device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, 
     const float* dec = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 3) * D;
     long long ck_off = 0;
     if (ck) ck_off = (long long)(c / p.ck_every_chunks) * p.ck_row_stride + (long long)x.h * STATE_ELEMS;
-#pragma unroll 1
-    for (int j = 0; j < 2; j++) {
-      const int col0 = 64 * hf + 32 * j;
-      uint32_t r[32];
-      tmem_ld32(tS + 32 * j, r);
-      tmem_wait_ld();
-      if (ck) {
-        if (p.ck_is_bf16) store_row_piece<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off, KF, v, col0, r);
-        else store_row_piece<float>(reinterpret_cast<float*>(task.ck) + ck_off, KF, v, col0, r);
-      }
-      if (last) {
-        if (task.dst != nullptr) store_row_piece<float>(task.dst + (size_t)x.h * STATE_ELEMS, KF, v, col0, r);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dec + col0 + 4 * i);
-          const float2 lo = mul2(make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), make_float2(d4.x, d4.y));
-          const float2 hi = mul2(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), make_float2(d4.z, d4.w));
-          r[4 * i] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
-          r[4 * i + 2] = __float_as_uint(hi.x); r[4 * i + 3] = __float_as_uint(hi.y);
-        }
-        tmem_st32(tS + 32 * j, r);
-      }
+    // Checkpoint rows and the final state leave tensor memory through an out-of-line routine, so that their register
+    // needs do not weigh on the per-chunk path below.
+    if (ck || last) {
+      float* dst = (last && task.dst != nullptr) ? task.dst + (size_t)x.h * STATE_ELEMS : nullptr;
+      void* ckp = nullptr;
+      if (ck) ckp = p.ck_is_bf16 ? static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off)
+                                 : static_cast<void*>(reinterpret_cast<float*>(task.ck) + ck_off);
+      store_state_rows<KF>(tS, dst, ckp, p.ck_is_bf16, v, hf);
     }
     if (last) break;
+    {
+      // The decay sits on the serial chain MMA1 -> decay -> MMA3 -> MMA1 of the next chunk: four 16-column pieces,
+      // the tensor-memory load of a piece in flight while the previous one is scaled and stored.
+      const float* dcol = dec + 64 * hf;
+      uint32_t a[16], b[16], e[16];
+      tmem_ld16(tS, a);
+      tmem_ld16(tS + 16, b);
+      tmem_wait_ld();
+      scale16(a, dcol);
+      tmem_st16(tS, a);
+      tmem_ld16(tS + 32, e);
+      scale16(b, dcol + 16);
+      tmem_st16(tS + 16, b);
+      tmem_ld16(tS + 48, a);
+      tmem_wait_ld();
+      scale16(e, dcol + 32);
+      tmem_st16(tS + 32, e);
+      scale16(a, dcol + 48);
+      tmem_st16(tS + 48, a);
+    }
     tmem_wait_st();
     tc_fence_before();
     __syncwarp();
