@@ -39,9 +39,9 @@ CK_EVERY = 1024
 FLOP_PER_TOKEN_HEAD = 6 * D * D + 4 * 64 * (D + D)          # 163 840, canonical chunk 64
 BYTES_PER_TOKEN_HEAD = 3 * D * 2 + D * 4 + 4 + D * 2         # q,k,v bf16 + g fp32 + beta fp32 + out bf16 = 1540
 METRIC = "KDA prefill tokens/s (H=64,K=V=128 varlen)"
-# dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_fwd_kernel per token-head, from the ncu capture of
+# dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_umma_kernel per token-head, from the ncu capture of
 # `bench.py --small` summarised under profiles/ (traffic grows in proportion to token-heads); None until captured.
-NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1688.3   # profiles/kda_chunk_umma_serving.md, section 2
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1701.6   # profiles/kda_chunk_umma_serving.md, section 2
 
 
 def workload_lengths(seed=2):
