@@ -438,6 +438,25 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
   for (int c = which; c < x.nchunks; c += 2) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
+    // Everything that does not depend on this chunk's L comes first, while the warp would only wait for L anyway (the
+    // v tile and the release of the stage by MMA3 of the chunk two back are normally long there): after the inversion
+    // only the operand write-out remains between L and MMA2.
+    // The v tile of a partial last chunk holds another sequence's rows (or worse) past the end of the run: zero them
+    // so that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  This warp observes every
+    // phase of the v barrier of its stage, so the wait cannot be satisfied by an older phase, and MMA2 waits for this
+    // warp's INV_FULL arrival.
+    x.wait(B_V_FULL + s, par, E_INV);
+    {
+      const int nvalid = min(C, x.len - c * C);
+      if (nvalid < C) {
+        uint8_t* vt = x.smem + OFF_CONS + s * CS_STAGE + CS_V;
+        for (int i = lane; i < (C - nvalid) * 16; i += 32) {     // whole 128-byte lines of both 64-channel halves
+          const int row = nvalid + (i >> 4), piece = i & 15;
+          *reinterpret_cast<uint4*>(vt + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
+    x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
     x.wait(B_L_FULL + s, par, E_INV);
     float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
     PROF_BEGIN;
@@ -494,22 +513,6 @@ __device__ void role_inverse(const Ctx& x, int which, int lane) {
     __syncwarp();
     const float* lbeta = reinterpret_cast<const float*>(x.smem + OFF_LBETA) + s * 32;
     PROF_STAMP(3, 26);
-    // The v tile of a partial last chunk holds another sequence's rows (or worse) past the end of the run: zero them
-    // so that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  This warp observes every
-    // phase of the v barrier of its stage, so the wait cannot be satisfied by an older phase, and MMA2 waits for this
-    // warp's INV_FULL arrival.
-    x.wait(B_V_FULL + s, par, E_INV);
-    {
-      const int nvalid = min(C, x.len - c * C);
-      if (nvalid < C) {
-        uint8_t* vt = x.smem + OFF_CONS + s * CS_STAGE + CS_V;
-        for (int i = lane; i < (C - nvalid) * 16; i += 32) {     // whole 128-byte lines of both 64-channel halves
-          const int row = nvalid + (i >> 4), piece = i & 15;
-          *reinterpret_cast<uint4*>(vt + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-    }
-    x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
     uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
     uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
     // Tb = T diag(beta): lane = row; eight columns (one 16-byte bf16 chunk, two 16-byte tf32 chunks) per step, the
