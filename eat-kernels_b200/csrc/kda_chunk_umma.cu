@@ -242,10 +242,13 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
 #pragma unroll
         for (int i = 0; i < 16; i++) a[i] = g[(16 * half + i) * D + ch] * LOG2E;
       } else {
+        // log2-decay = lower_bound log2(e) sigmoid(x), x = exp(A_log) (g + dt_bias); sigmoid(x) = 1 / (1 + 2^(-x log2 e))
+        // with the exponent argument formed by one fused multiply-add per element
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(raw + RAW_G);
         const float c2 = p.lower_bound * LOG2E;
+        const float m1 = -LOG2E * eA, m0 = m1 * dtb;
 #pragma unroll
-        for (int i = 0; i < 16; i++) a[i] = c2 * sigmoidf_rel(eA * (__bfloat162float(g[(16 * half + i) * D + ch]) + dtb));
+        for (int i = 0; i < 16; i++) a[i] = c2 * rcpf(1.0f + ex2f(fmaf(__bfloat162float(g[(16 * half + i) * D + ch]), m1, m0)));
       }
 #pragma unroll
       for (int i = 0; i < 16; i++) {
