@@ -179,7 +179,8 @@ def run_longctx(args, world, rank, dev, kda_b200):
     import torch.distributed as dist
     from kda_b200 import parallel
     T_total, H = 131072, 96
-    T = T_total // world
+    shards = parallel.balanced_shards(T_total, world, H) if not args.equal_shards else [T_total // world] * world
+    T = shards[rank]
     gen = torch.Generator(device=dev).manual_seed(200 + rank)
     q = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
     k = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
@@ -224,7 +225,7 @@ def run_longctx(args, world, rank, dev, kda_b200):
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "configs[3]: T=131072, H=96, g=logsigmoid(N(2,1)), zero initial state", "pieces_per_rank": pieces,
-                       "parallelism": f"cp{world}", "finite": finite},
+                       "tokens_per_rank": shards, "parallelism": f"cp{world}", "finite": finite},
             "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
             "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
@@ -248,6 +249,7 @@ def main(argv=None):
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
     ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = chosen by a wave model)")
+    ap.add_argument("--equal-shards", action="store_true", help="longctx: equal token shards instead of cost-balanced ones")
     args = ap.parse_args(argv)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     lens = workload_lengths()

@@ -69,6 +69,36 @@ def choose_pieces(T, H, first_rank, n_sms=148, max_pieces=8):
     return best
 
 
+def segment_cost(T, H, first_rank, n_sms=148, max_pieces=8):
+    """Makespan of a rank's segment launch in chunk steps under the wave model of `choose_pieces`."""
+    nchunks = -(-T // CHUNK)
+    if nchunks <= 0:
+        return 0
+    p = choose_pieces(T, H, first_rank, n_sms, max_pieces)
+    ctas = H * (2 * p - (1 if first_rank else 0))
+    return -(-ctas // n_sms) * -(-nchunks // p)
+
+
+def balanced_shards(T, world, H, n_sms=148, max_pieces=8):
+    """Token counts per rank (chunk-aligned, in rank order, summing to T) for context parallelism.  Rank 0 runs the plain
+    chain on its first piece while every other piece runs two chains, so equal shards leave rank 0 idle; the shards
+    are sized inversely to each rank's cost per chunk in the wave model (the reference cuts unequal segments for the
+    same reason, kda/b200/csrc/w3/kernel.py:22-38)."""
+    nch = -(-T // CHUNK)
+    if world <= 1 or nch < world:
+        return [T] + [0] * (world - 1)
+    eq = nch // world
+    inv = []
+    for r in range(world):
+        inv.append(eq / max(1, segment_cost(eq * CHUNK, H, r == 0, n_sms, max_pieces)))
+    tot = sum(inv)
+    chunks = [max(1, int(nch * x / tot)) for x in inv]
+    chunks[0] += nch - sum(chunks)
+    shards = [c * CHUNK for c in chunks]
+    shards[-1] -= nch * CHUNK - T          # the last chunk of the sequence may be partial
+    return shards
+
+
 class CudaBackend:
     """The shipped backend: the three context-parallel steps on the current CUDA device through the C ABI."""
 

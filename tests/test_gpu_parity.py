@@ -79,6 +79,14 @@ def test_other_heads_and_tiny(kda, H, lens):
     _plain_case(kda, H, lens, 500 + H)
 
 
+@pytest.mark.parametrize("H,lens", [(4, [64] * 512), (2, [random.Random(7).randint(1, 300) for _ in range(200)]),
+                                    (3, [1] * 70 + [2048] + [1] * 70)])
+def test_many_short_sequences(kda, H, lens):
+    """Layouts with far more (sequence, head) tasks than SMs, most of them one or two chunks long (the 512 x 64 layout
+    of the single-graph configuration), and single-token runs next to a long one."""
+    _plain_case(kda, H, lens, 600 + H)
+
+
 def test_single_sequence_no_cu(kda):
     inputs = ko.make_inputs_raw(16, [1500], 600)
     gold_o, gold_s, _ = gold_raw(inputs, [1500])

@@ -109,6 +109,16 @@ def test_split_pieces_and_head_slice():
     assert parallel.choose_pieces(16384, 96, True) == 1
     assert parallel.choose_pieces(16384, 96, False) == 3
     assert parallel.choose_pieces(32, 4, False) == 1
+    # cost-balanced shards: chunk-aligned, in order, sum to T, and a smaller makespan than the equal split
+    for world in (2, 4, 8):
+        sh = parallel.balanced_shards(131072, world, 96)
+        assert sum(sh) == 131072 and all(x % 32 == 0 and x > 0 for x in sh) and sh[0] > sh[1]
+        bal = max(parallel.segment_cost(t, 96, i == 0) for i, t in enumerate(sh))
+        eq = max(parallel.segment_cost(131072 // world, 96, i == 0) for i in range(world))
+        assert bal < eq
+    assert parallel.balanced_shards(1000, 1, 4) == [1000]
+    sh = parallel.balanced_shards(1000, 3, 4)
+    assert sum(sh) == 1000 and all(x % 32 == 0 for x in sh[:-1])
 
 
 def _hp_worker(rank, world, port, ret):
