@@ -243,6 +243,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-groups", type=int, default=6, help="end-to-end arm: request groups whose copies and prefills overlap")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
     ap.add_argument("--workload", default="serving", choices=["serving", "longctx"],
@@ -317,23 +318,61 @@ def main(argv=None):
         ms = float(t.item())
     clocks = sampler.stop() if sampler else None
 
-    # ---- end to end through the public call with HOST buffers: pinned inputs -> device -> prefill -> output to host
+    # ---- end to end through the public call with HOST buffers: pinned inputs -> device -> prefill -> output to host.
+    # The requests are served in a few groups of consecutive sequences, each with its own prepared launch over slices of
+    # the same buffers, so that the host-to-device copy of the next group, the prefill of the current one and the
+    # device-to-host copy of the previous one overlap (the step is bound by the PCIe link, which is full duplex).
     e2e = None
     if args.e2e_steps > 0:
-        host = [t.cpu().pin_memory() for t in (q, k, v, g, beta, cu, slots, ck_starts)]
-        devs = [q, k, v, g, beta, cu, slots, ck_starts]
+        n_groups = max(1, min(args.e2e_groups, N))
+        target, acc, cuts = T / n_groups, 0, [0]
+        for i, n in enumerate(lens):
+            acc += n
+            if acc >= target * len(cuts) and len(cuts) < n_groups and i + 1 < N:
+                cuts.append(i + 1)
+        cuts.append(N)
+        cu_l, ck_l = [0, *torch.tensor(lens).cumsum(0).tolist()], [0, *torch.tensor(counts).cumsum(0).tolist()]
+        groups, h2d = [], 0
+        for a_, b_ in zip(cuts[:-1], cuts[1:]):
+            ta, tb, ra, rb = cu_l[a_], cu_l[b_], ck_l[a_], ck_l[b_]
+            dv = [q[:, ta:tb], k[:, ta:tb], v[:, ta:tb], g[:, ta:tb], beta[:, ta:tb],
+                  (cu[a_:b_ + 1] - cu[a_]).contiguous(), slots[a_:b_].contiguous(), (ck_starts[a_:b_ + 1] - ck_starts[a_]).contiguous()]
+            hv = [t.cpu().pin_memory() for t in dv]
+            h2d += sum(t.numel() * t.element_size() for t in hv)
+            lg = kda_b200.prepare_plain(dv[0], dv[1], dv[2], dv[3], dv[4], D ** -0.5, pool, False, dv[5], dynamic_layout=True,
+                                        ssm_state_indices=dv[6], state_checkpoints=ck[ra:rb], checkpoint_cu_starts=dv[7],
+                                        checkpoint_every_n_tokens=CK_EVERY)
+            groups.append((dv, hv, lg, ta, tb))
         out_host = torch.empty((1, T, H, D), dtype=torch.bfloat16).pin_memory()
-        h2d = sum(t.numel() * t.element_size() for t in host)
         d2h = out_host.numel() * out_host.element_size()
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        main = torch.cuda.current_stream(dev)
 
         def step():
-            for d_, h_ in zip(devs, host):
-                d_.copy_(h_, non_blocking=True)
-            res = launch()
-            out_host.copy_(res[0], non_blocking=True)
+            s_in.wait_stream(main)                       # the previous step's prefills have read the input buffers
+            done = []
+            for dv, hv, lg, ta, tb in groups:
+                with torch.cuda.stream(s_in):
+                    for d_, h_ in zip(dv, hv):
+                        d_.copy_(h_, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                main.wait_event(ev)
+                res = lg()
+                ev2 = torch.cuda.Event()
+                ev2.record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev2)
+                    out_host[:, ta:tb].copy_(res[0], non_blocking=True)
+                done.append(res)
+            main.wait_stream(s_out)
+            return done
 
         step()
         barrier()
+        for dv, hv, lg, ta, tb in groups:
+            if kda_b200.status_bits(lg) != 0 or kda_b200.kernel_error(lg) != 0:
+                raise SystemExit("bench: an end-to-end launch reported a table or kernel error")
         e0.record()
         for _ in range(args.e2e_steps):
             step()
@@ -345,7 +384,7 @@ def main(argv=None):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ems = float(t.item())
         e2e = {"value": T / (ems * 1e-3), "unit": "tokens/s", "ms_per_step": ems, "h2d_bytes_per_step": h2d * world,
-               "d2h_bytes_per_step": d2h * world}
+               "d2h_bytes_per_step": d2h * world, "groups": len(groups)}
 
     if rank == 0:
         pk = peaks()
