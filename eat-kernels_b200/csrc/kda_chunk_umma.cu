@@ -1,7 +1,7 @@
 // Fused KDA chunk kernel on the 5th-generation tensor core (tcgen05 + tensor memory), sm_100a.
 //
 // One CTA walks the 32-token chunks of one (token run, head) task.  The fp32 state St [V=128][K=128] (value-first) never
-// leaves tensor memory between chunks, and the whole per-chunk chain is tensor-core work issued by one thread:
+// leaves tensor memory between chunks, and the whole per-chunk chain is tensor-core work issued by one elected lane:
 //
 //   MMA1  [W | O] = St [kd ; qd]^T          tf32: A = St read straight from its accumulator columns, N = 64, K = 128
 //   MMA2  U  = v^T Tbh^T - W Tb^T           bf16 (A = v tile, MN-major) then tf32 (A = W columns, B negated), N = 32, K = 32
@@ -11,17 +11,20 @@
 // M = tril(qd' ki'^T) (G = inclusive cumulative log2-decay of the chunk; primed operands are taken relative to the
 // exponent after token 15 so that every exponent is bounded by the decay of 16 tokens).  This is the chunked form of
 // kda/b200/reference.py:30-37.  No accumulator makes a round trip through registers on the chain; the only register
-// pass is the per-chunk decay St <- St diag(2^G31), done by four "scaler" warps between MMA1 and MMA3, off the MMA
-// thread's issue path.  Because tf32 operands keep 10 mantissa bits, the state enters the products more accurately
+// pass is the per-chunk decay St <- St diag(2^G31), done by the eight tensor-memory warps between MMA1 and MMA3, off
+// the MMA warp's issue path.  Because tf32 operands keep 10 mantissa bits, the state enters the products more accurately
 // than a bf16 copy would.
 //
-// Warp roles (28 warps): 0 MMA issuer (+ tensor-memory allocation), 1-2 triangular inverse (alternating chunks),
-// 3 loader (one lane polls three TMA copy streams g / q,k / v; v goes straight into the consumer stage), 4-11 tensor-memory
-// warps (state load / per-chunk decay / checkpoints / final store, and O -> bf16 -> global; each warp serves half of
-// the columns of one lane quarter), 12-27 operand preparation in two groups of eight
-// warps that alternate chunks (gate + cumsum, L2 norm, decayed operand tiles, intra-chunk products on mma.sync).  Roles hand off through mbarriers; every wait is bounded
-// (see kda_umma.cuh): on a timeout the CTA keeps its control flow, drains, frees tensor memory and reports an error
-// code in status[2].
+// Warp roles (28 warps):
+//    0      MMA issuer (+ tensor-memory allocation); the whole warp runs the issue loop on warp-uniform values
+//    1-2    triangular inverse, alternating chunks
+//    3      loader: one lane polls three TMA copy streams (g / q,k / v); v goes straight into the consumer stage
+//    4-11   tensor-memory warps: state load, per-chunk decay, checkpoints, final store, and O -> bf16 -> global; each
+//           warp serves half of the columns of one lane quarter
+//    12-27  operand preparation in two groups of eight warps that alternate chunks: gate + cumsum, L2 norm, decayed
+//           operand tiles, intra-chunk products on mma.sync
+// Roles hand off through mbarriers; every wait is bounded (see kda_umma.cuh): on a timeout the CTA keeps its control
+// flow, drains, frees tensor memory and reports an error code in status[2].
 #include "kda_common.cuh"
 #include "kda_plan.cuh"
 #include "kda_tma.cuh"
@@ -604,7 +607,7 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
     for (int ks = 0; ks < 4; ks++)                        // O += U M^T does not touch the state: issued before the wait
       mma_ts_tf32_pred(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
     mma_commit_pred(x.bar(B_O_FULL + s), go);
-    x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0); // scaler finished St <- St diag(2^G31)
+    x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0); // decay St <- St diag(2^G31) finished
     tc_fence_after();
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
@@ -618,7 +621,7 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
   x.wait(B_DRAIN, 0, E_MMA, 0);
 }
 
-// ------------------------------------------------------------------------------------------------ scaler warps
+// ------------------------------------------------------------------------------------------------ tensor-memory warps
 template <typename OutT>
 __device__ __forceinline__ void store_row_piece(OutT* dst_head, int key_first, int v, int col0, const uint32_t (&r)[32]);
 
