@@ -216,6 +216,13 @@ def run_longctx(args, world, rank, dev, kda_b200):
         ms = float(t.item())
     finite = bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(fin).all())
     clocks = sampler.stop() if sampler else None
+    # one more step with CUDA events at the phase boundaries (this rank's view; not part of the timed region)
+    ev = []
+    parallel.context_parallel_prefill(q, k, v, g, beta, None, None, D ** -0.5, None, pieces=pieces, raw=False, backend=be, events=ev)
+    torch.cuda.synchronize()
+    phases = {b[0]: round(a[1].elapsed_time(b[1]), 4) for a, b in zip(ev[:-1], ev[1:])}
+    mapped_tokens = T - (parallel.split_pieces(T, pieces)[1] if rank == 0 else 0)
+    fix_bytes = mapped_tokens * H * 3 * D * 2 + (pieces - (1 if rank == 0 else 0)) * H * D * D * 4
     if rank == 0:
         pk = peaks()
         flops = T_total * H * FLOP_PER_TOKEN_HEAD
@@ -230,6 +237,9 @@ def run_longctx(args, world, rank, dev, kda_b200):
                          "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
             "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
                        "frac": flops / (ms * 1e-3) / 1e12 / pk["tf"]},
+            "phases_ms_rank0": phases,
+            "fixup": {"bytes": fix_bytes, "GB/s": (fix_bytes / (phases["fixup"] * 1e-3) / 1e9) if phases.get("fixup", 0) > 0 else None,
+                      "note": "o_loc + Qt read, out written (768 B per mapped token-head) plus the entering states"},
             "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()

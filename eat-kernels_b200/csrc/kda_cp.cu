@@ -98,9 +98,12 @@ cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, flo
 
 // ------------------------------------------------------------------------------------------------ output fix-up
 // out[t][h][:] += bf16(S_in[seg][h]) applied to Qt[t][h][:] for the tokens of mapped segments.  A CTA owns one
-// (segment, head, slice): it converts the entering state to a swizzled bf16 tile once and walks 32-token tiles.
+// (segment, head, slice): it converts the entering state to a swizzled bf16 tile once and walks 32-token tiles.  Both
+// the Qt tile and the old output tile come in through cp.async as whole 256-byte rows, the sum is formed in shared
+// memory and leaves as whole rows again: the pass is pure HBM traffic (768 B per token-head), so every global access
+// is a full line.
 constexpr int FIX_THREADS = 256;
-constexpr int FIX_SMEM = 32768 + 2 * 8192;   // bf16 state [128][128] + double-buffered Qt tile [32][128]
+constexpr int FIX_SMEM = 32768 + 2 * 16384;  // bf16 state [128][128] + double-buffered {Qt tile, output tile} [32][128]
 
 __global__ void __launch_bounds__(FIX_THREADS) kda_fixup_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ qt,
                                                                 long long ldo, const float* __restrict__ S_in,
@@ -131,12 +134,15 @@ __global__ void __launch_bounds__(FIX_THREADS) kda_fixup_kernel(__nv_bfloat16* _
   auto issue = [&](int tile, int buf) {
     const long long tok0 = t0 + (long long)tile * 32;
     const int nvalid = (int)min(32LL, t1 - tok0);
-    const uint32_t dst = smem_u32(smem + 32768 + buf * 8192);
+    const uint32_t dst = smem_u32(smem + 32768 + buf * 16384);
 #pragma unroll
     for (int j = 0; j < 2; j++) {
       const int idx = tid + FIX_THREADS * j, row = idx >> 4, ch = idx & 15;
       const bool ok = row < nvalid;
-      cp_async16(dst + row * 256 + ((ch ^ (row & 7)) << 4), qt + (tok0 + (ok ? row : 0)) * ldo + (long long)h * D + ch * 8, ok ? 16 : 0);
+      const long long goff = (tok0 + (ok ? row : 0)) * ldo + (long long)h * D + ch * 8;
+      const uint32_t soff = row * 256 + ((ch ^ (row & 7)) << 4);
+      cp_async16(dst + soff, qt + goff, ok ? 16 : 0);
+      cp_async16(dst + 8192 + soff, out + goff, ok ? 16 : 0);
     }
   };
   issue(slice, 0);
@@ -147,7 +153,8 @@ __global__ void __launch_bounds__(FIX_THREADS) kda_fixup_kernel(__nv_bfloat16* _
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const uint32_t q_tile = smem_u32(smem + 32768 + buf * 8192);
+    const uint32_t q_tile = smem_u32(smem + 32768 + buf * 16384);
+    uint8_t* o_tile = smem + 32768 + buf * 16384 + 8192;
     float acc[2][2][4];
 #pragma unroll
     for (int a = 0; a < 2; a++)
@@ -174,15 +181,21 @@ __global__ void __launch_bounds__(FIX_THREADS) kda_fixup_kernel(__nv_bfloat16* _
 #pragma unroll
       for (int half = 0; half < 2; half++) {
         const int row = 16 * mt + g + 8 * half;
-        if (row < nvalid) {
 #pragma unroll
-          for (int nt = 0; nt < 2; nt++) {
-            uint32_t* o = reinterpret_cast<uint32_t*>(out + (tok0 + row) * ldo + (long long)h * D + 16 * warp + 8 * nt + 2 * t);
-            const uint32_t old = *o;
-            *o = pack_bf16(bf16_lo(old) + acc[mt][nt][2 * half], bf16_hi(old) + acc[mt][nt][2 * half + 1]);
-          }
+        for (int nt = 0; nt < 2; nt++) {
+          uint32_t* o = reinterpret_cast<uint32_t*>(o_tile + tile128_off(row, 16 * warp + 8 * nt + 2 * t));
+          const uint32_t old = *o;
+          *o = pack_bf16(bf16_lo(old) + acc[mt][nt][2 * half], bf16_hi(old) + acc[mt][nt][2 * half + 1]);
         }
       }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int idx = tid + FIX_THREADS * j, row = idx >> 4, ch = idx & 15;
+      if (row < nvalid)
+        *reinterpret_cast<uint4*>(out + (tok0 + row) * ldo + (long long)h * D + ch * 8) =
+            *reinterpret_cast<const uint4*>(o_tile + row * 256 + ((ch ^ (row & 7)) << 4));
+    }
     __syncthreads();
   }
 }

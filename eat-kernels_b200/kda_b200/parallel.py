@@ -183,15 +183,23 @@ def compose_rank_map(backend, P, S_loc):
 
 
 def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_state=None, *, group=None, pieces=0,
-                             raw=True, backend=None):
+                             raw=True, backend=None, events=None):
     """Context-parallel prefill of ONE sequence whose tokens are sharded over the ranks of `group` in rank order.
 
     q, k, v, g [1, T_local, H, 128] and beta [1, T_local, H] are this rank's shard (contiguous token rows);
     initial_state [1, H, 128, 128] fp32 value-first is read on rank 0 (zeros when None).  With `group=None` (or a
     single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.  `pieces=0` picks the
     piece count per rank from a wave model of the segment launch (`choose_pieces`).
+    `events`, when a list, receives (phase name, CUDA event) pairs recorded on the current stream at the phase
+    boundaries ("start", "segments", "maps", "exchange", "scan", "fixup"), for callers that time the phases.
     Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank)."""
     import torch.distributed as dist
+
+    def mark(name):
+        if events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            events.append((name, e))
 
     world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
     rank = dist.get_rank(group) if world > 1 else 0
@@ -206,9 +214,12 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     if rank == 0:
         need_map[0] = 0            # the first piece of the sequence starts from the caller's state: plain chain
         first = initial_state if initial_state is not None else torch.zeros(1, H, D, D, dtype=torch.float32, device=q.device)
+    mark("start")
     out, qt, P, S_loc = backend.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first)
+    mark("segments")
     # P of an unmapped piece is the zero map (its S_loc is the true end state): segment_maps leaves it zero-filled
     P_rank, L_rank = compose_rank_map(backend, P, S_loc)
+    mark("maps")
     if world > 1:
         mine = torch.stack([P_rank, L_rank])                               # [2, H, 128, 128]
         gathered = torch.empty(world, *mine.shape, dtype=mine.dtype, device=mine.device)
@@ -218,6 +229,9 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     else:
         S_enter = None
         S_final = L_rank
+    mark("exchange")
     S_in, _ = backend.scan(P, S_loc, S_enter)
+    mark("scan")
     out = backend.fixup(out, qt, S_in, bounds, need_map)
+    mark("fixup")
     return out, S_final[None]
