@@ -87,6 +87,18 @@ def test_many_short_sequences(kda, H, lens):
     _plain_case(kda, H, lens, 600 + H)
 
 
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_layout_sweep(kda, seed):
+    """Randomised layouts against the fp64 recurrence: head counts, sequence counts and lengths drawn per case (short and
+    partial chunks, odd / even chunk counts, single tokens), slow gates in a third of the cases."""
+    rng = random.Random(seed)
+    for case in range(12):
+        H = rng.choice([1, 2, 3, 5, 8])
+        n = rng.randint(1, 10)
+        lens = [rng.choice([1, 31, 32, 33, 64, 65]) if rng.random() < 0.3 else rng.randint(1, 400) for _ in range(n)]
+        _plain_case(kda, H, lens, 1000 * seed + case, slow=(case % 3 == 2), static=bool(case & 1))
+
+
 def test_single_sequence_no_cu(kda):
     inputs = ko.make_inputs_raw(16, [1500], 600)
     gold_o, gold_s, _ = gold_raw(inputs, [1500])
