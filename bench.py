@@ -178,7 +178,7 @@ def run_longctx(args, world, rank, dev, kda_b200):
     tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up."""
     import torch.distributed as dist
     from kda_b200 import parallel
-    T_total, H = 131072, 96
+    T_total, H = args.longctx_tokens, 96
     shards = parallel.balanced_shards(T_total, world, H) if not args.equal_shards else [T_total // world] * world
     T = shards[rank]
     gen = torch.Generator(device=dev).manual_seed(200 + rank)
@@ -228,10 +228,10 @@ def run_longctx(args, world, rank, dev, kda_b200):
         flops = T_total * H * FLOP_PER_TOKEN_HEAD
         algo_bytes = T_total * H * BYTES_PER_TOKEN_HEAD + H * 2 * D * D * 4
         print(json.dumps({
-            "metric": "KDA prefill tokens/s (H=96,K=V=128, one 131072-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
+            "metric": f"KDA prefill tokens/s (H=96,K=V=128, one {T_total}-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[3]: T=131072, H=96, g=logsigmoid(N(2,1)), zero initial state", "pieces_per_rank": pieces,
+            "config": {"workload": f"configs[3]: T={T_total}, H=96, g=logsigmoid(N(2,1)), zero initial state", "pieces_per_rank": pieces,
                        "tokens_per_rank": shards, "parallelism": f"cp{world}", "finite": finite},
             "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
@@ -261,6 +261,7 @@ def main(argv=None):
                          "sequence at H=96, context-parallel over the ranks")
     ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = chosen by a wave model)")
     ap.add_argument("--equal-shards", action="store_true", help="longctx: equal token shards instead of cost-balanced ones")
+    ap.add_argument("--longctx-tokens", type=int, default=131072, help="longctx: sequence length (smaller values for profiler captures)")
     args = ap.parse_args(argv)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     lens = workload_lengths()
