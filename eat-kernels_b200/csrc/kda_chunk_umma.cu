@@ -37,7 +37,7 @@ namespace u {
 
 constexpr int WARPS = 28;
 constexpr int THREADS = WARPS * 32;
-constexpr int W_MMA = 0, W_INV0 = 1, W_LOAD = 3, W_SCALE0 = 4, W_EPI0 = 8, W_PREP0 = 12;
+constexpr int W_MMA = 0, W_INV0 = 1, W_LOAD = 3, W_SCALE0 = 4, W_PREP0 = 12;
 constexpr int PREP_GROUPS = 2;                 // group g prepares the chunks c with c % 2 == g, in stage g
 constexpr int PREP_WARPS = 8, PREP_THREADS = 256;   // per group
 
@@ -108,16 +108,6 @@ struct Ctx {
   __device__ __forceinline__ void wait(int i, uint32_t parity, int code, unsigned sleep_ns = kSleepNs) const {
     mbar_wait(bar(i), parity, abort_flag, code + i, sleep_ns);
   }
-#endif
-  // for a single elected thread (the MMA issuer)
-#ifdef KDA_PROF
-  __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const {
-    const long long t = clock64();
-    mbar_wait(bar(i), parity, abort_flag, code + i);
-    if (blockIdx.x == 0) atomicAdd(prof + ((code >> 4) * 64 + i), (unsigned long long)(clock64() - t));
-  }
-#else
-  __device__ __forceinline__ void wait1(int i, uint32_t parity, int code) const { mbar_wait(bar(i), parity, abort_flag, code + i); }
 #endif
 };
 

@@ -52,12 +52,6 @@ __device__ __forceinline__ void load_3d(uint32_t dst, const CUtensorMap* map, in
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
                :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void prefetch_3d(const CUtensorMap* map, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n" :: "l"(map), "r"(x), "r"(y), "r"(z) : "memory");
-}
-__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];\n" :: "l"(map) : "memory");
-}
 
 }  // namespace tma
 #endif

@@ -1,7 +1,7 @@
 // tcgen05 / TMEM / mbarrier primitives for sm_100a, as thin inline-PTX wrappers.
 //
 // Conventions used by the KDA kernels:
-//   * cta_group::1 only; one elected thread issues tcgen05.mma and tcgen05.commit.
+//   * cta_group::1 only; one elected lane issues tcgen05.mma and tcgen05.commit, predicated inside a warp-convergent loop.
 //   * Shared-memory operands use the canonical swizzled layouts of the 5th-generation tensor core:
 //       K-major  SW128: rows (M or N index) of 128 bytes of K, 8-row groups 1024 B apart (SBO), 16-byte chunks of a
 //                       row XOR-swizzled with (row % 8); a K slice of one instruction is 32 bytes and is selected by
@@ -43,14 +43,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds before it reports failure, so a
-// waiting warp does not compete for issue slots with the warps it is waiting for
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
@@ -81,13 +73,6 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, unsigned sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, code, sleep_ns);
-}
-// Bounded wait of a converged warp: lane 0 waits, the other lanes sleep at the warp barrier and then observe the
-// completed phase themselves (one successful poll each), which gives every lane its own acquire.
-__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if ((threadIdx.x & 31) == 0) mbar_wait(bar, parity, abort_flag, code);
-  __syncwarp();
-  (void)mbar_try_wait(bar, parity);
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operand reads)
@@ -165,23 +150,6 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
 }
 
 // ---------------------------------------------------------------------------------------------- MMA issue
-// D (tensor memory) (+)= A (shared memory) * B (shared memory)
-__device__ __forceinline__ void mma_ss_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// D (tensor memory) (+)= A (tensor memory, fp32 columns read as tf32) * B (shared memory, tf32)
-__device__ __forceinline__ void mma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
-               :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// mbarrier arrives once every tcgen05.mma issued so far by this thread has completed
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(bar) : "memory");
-}
-
 // Warp-convergent issue.  The tensor-core instructions take their descriptors and addresses from warp-uniform
 // registers.  When the issuing code sits inside a one-lane branch the compiler has to move every operand from a
 // vector register into a uniform one right before each instruction, which serialises at roughly 50 cycles per
@@ -193,16 +161,19 @@ __device__ __forceinline__ uint32_t elect_one() {
   asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
   return pred;
 }
+// D (tensor memory) (+)= A (shared memory) * B (shared memory), bf16 operands
 __device__ __forceinline__ void mma_ss_f16_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint32_t go) {
   asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %5, 0;\n"
                " @q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go) : "memory");
 }
+// D (tensor memory) (+)= A (tensor memory, fp32 columns read as tf32) * B (shared memory, tf32)
 __device__ __forceinline__ void mma_ts_tf32_pred(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint32_t go) {
   asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %5, 0;\n"
                " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
                :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go) : "memory");
 }
+// the mbarrier receives one arrival once every tcgen05.mma issued so far by the elected lane has completed
 __device__ __forceinline__ void mma_commit_pred(uint32_t bar, uint32_t go) {
   asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n"
                " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" :: "r"(bar), "r"(go) : "memory");
