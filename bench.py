@@ -414,7 +414,7 @@ def main(argv=None):
                        "l2": "inputs (GBs per step) far exceed L2; no flush needed", "parallelism": f"hp{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],
-                         "kernel": "kda_chunk_umma_kernel (the step also holds kda_plan_kernel, 0.65 % of the time)",
+                         "kernel": "kda_chunk_umma_kernel (the step also holds kda_plan_kernel, 0.9 % of the time)",
                          "algorithmic_bytes_per_launch": algo_bytes},
             "tensor": {"achieved": tf, "peak": pk["tf"], "unit": "TFLOP/s", "frac": tf / pk["tf"],
                        "flops_per_launch": flops, "note": "dense count 163840 FLOP per token-head (chunk 64 convention)"},
