@@ -187,7 +187,7 @@ def run_longctx(args, world, rank, dev, kda_b200):
     v = torch.randn(1, T, H, D, generator=gen, device=dev).to(torch.bfloat16)
     g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=dev) + 2.0)
     beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=dev))
-    pieces = args.pieces or parallel.choose_pieces(T, H, rank == 0)
+    pieces = args.pieces            # 0: the library plans the piece boundaries by simulating the segment launch
     be = parallel.CudaBackend()
 
     def step():
@@ -221,8 +221,9 @@ def run_longctx(args, world, rank, dev, kda_b200):
     parallel.context_parallel_prefill(q, k, v, g, beta, None, None, D ** -0.5, None, pieces=pieces, raw=False, backend=be, events=ev)
     torch.cuda.synchronize()
     phases = {b[0]: round(a[1].elapsed_time(b[1]), 4) for a, b in zip(ev[:-1], ev[1:])}
-    mapped_tokens = T - (parallel.split_pieces(T, pieces)[1] if rank == 0 else 0)
-    fix_bytes = mapped_tokens * H * 3 * D * 2 + (pieces - (1 if rank == 0 else 0)) * H * D * D * 4
+    bounds = parallel.plan_bounds(T, H, rank == 0) if pieces <= 0 else parallel.split_pieces(T, pieces)
+    mapped_tokens = T - (bounds[1] if rank == 0 else 0)
+    fix_bytes = mapped_tokens * H * 3 * D * 2 + (len(bounds) - 1 - (1 if rank == 0 else 0)) * H * D * D * 4
     if rank == 0:
         pk = peaks()
         flops = T_total * H * FLOP_PER_TOKEN_HEAD
@@ -231,7 +232,7 @@ def run_longctx(args, world, rank, dev, kda_b200):
             "metric": f"KDA prefill tokens/s (H=96,K=V=128, one {T_total}-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"configs[3]: T={T_total}, H=96, g=logsigmoid(N(2,1)), zero initial state", "pieces_per_rank": pieces,
+            "config": {"workload": f"configs[3]: T={T_total}, H=96, g=logsigmoid(N(2,1)), zero initial state", "piece_bounds_rank0": bounds,
                        "tokens_per_rank": shards, "parallelism": f"cp{world}", "finite": finite},
             "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},

@@ -23,6 +23,7 @@ on CPU ranks with a stand-in backend supplied by the tests; the package itself s
 from __future__ import annotations
 
 import ctypes as C
+import functools
 
 import torch
 
@@ -69,14 +70,59 @@ def choose_pieces(T, H, first_rank, n_sms=148, max_pieces=8):
     return best
 
 
+def _makespan(costs, n_sms):
+    """Longest-first list scheduling of task costs on n_sms workers (what the hardware block scheduler does with a
+    grid whose CTAs are ordered by decreasing length)."""
+    import heapq
+    heap = [0.0] * n_sms
+    for c in sorted(costs, reverse=True):
+        heapq.heapreplace(heap, heap[0] + c)
+    return max(heap)
+
+
+def plan_bounds(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_steps_per_chunk_head=0.0025):
+    """Piece boundaries of one rank's shard (see `_plan`, which also returns the simulated cost)."""
+    return list(_plan(T, H, first_rank, n_sms, max_pieces, task_overhead, fixup_steps_per_chunk_head)[0])
+
+
+@functools.lru_cache(maxsize=256)        # the search costs milliseconds on the host; layouts repeat call after call
+def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_steps_per_chunk_head=0.0025):
+    """Piece boundaries (chunk-aligned token offsets, first 0, last T) of one rank's shard, chosen by simulating the
+    segment launch: every mapped piece is two tasks per head (chains L and Tr), the first piece of the first rank one
+    plain task per head; a task costs its chunks plus `task_overhead` chunk steps, and mapped tokens cost a fix-up pass.
+    On the first rank the plain first piece may be LONGER than the mapped pieces: while its H CTAs run, the remaining
+    SMs work through the doubled chains of the shorter pieces (with H = 96 on 148 SMs the plain chain alone would
+    leave a third of the GPU idle)."""
+    nch = -(-T // CHUNK)
+    if nch <= 1:
+        return [0, T], float(nch) + task_overhead
+    best, best_cost = [0, nch], None
+    firsts = sorted({nch} | {max(1, int(nch * f / 16)) for f in range(1, 16)}) if first_rank else [0]
+    for c_first in firsts:
+        rest = nch - c_first
+        for m in range(0, max_pieces + 1):
+            if (m == 0) != (rest == 0) or m > rest:      # m mapped pieces share the `rest` chunks (none when rest = 0)
+                continue
+            base, extra = divmod(rest, m) if m else (0, 0)
+            pieces = [base + (1 if i < extra else 0) for i in range(m)]
+            costs = [c_first + task_overhead] * H if c_first else []
+            for c in pieces:
+                costs += [c + task_overhead] * (2 * H)
+            cost = _makespan(costs, n_sms) + fixup_steps_per_chunk_head * rest * H
+            if best_cost is None or cost < best_cost - 1e-9:
+                cuts, acc = [0], 0
+                for c in ([c_first] if c_first else []) + pieces:
+                    acc += c
+                    cuts.append(acc)
+                best, best_cost = cuts, cost
+    return [min(T, c * CHUNK) for c in best], best_cost
+
+
 def segment_cost(T, H, first_rank, n_sms=148, max_pieces=8):
-    """Makespan of a rank's segment launch in chunk steps under the wave model of `choose_pieces`."""
-    nchunks = -(-T // CHUNK)
-    if nchunks <= 0:
-        return 0
-    p = choose_pieces(T, H, first_rank, n_sms, max_pieces)
-    ctas = H * (2 * p - (1 if first_rank else 0))
-    return -(-ctas // n_sms) * -(-nchunks // p)
+    """Simulated makespan of a rank's segment launch and fix-up, in chunk steps (see `plan_bounds`)."""
+    if T <= 0:
+        return 0.0
+    return _plan(T, H, first_rank, n_sms, max_pieces)[1]
 
 
 def balanced_shards(T, world, H, n_sms=148, max_pieces=8):
@@ -188,8 +234,8 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
 
     q, k, v, g [1, T_local, H, 128] and beta [1, T_local, H] are this rank's shard (contiguous token rows);
     initial_state [1, H, 128, 128] fp32 value-first is read on rank 0 (zeros when None).  With `group=None` (or a
-    single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.  `pieces=0` picks the
-    piece count per rank from a wave model of the segment launch (`choose_pieces`).
+    single rank) this is intra-GPU context parallelism: the pieces only serve to fill the SMs.  `pieces=0` plans the
+    piece boundaries by simulating the segment launch (`plan_bounds`); `pieces=n` cuts n equal pieces.
     `events`, when a list, receives (phase name, CUDA event) pairs recorded on the current stream at the phase
     boundaries ("start", "segments", "maps", "exchange", "scan", "fixup"), for callers that time the phases.
     Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank)."""
@@ -205,9 +251,7 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     rank = dist.get_rank(group) if world > 1 else 0
     backend = backend or CudaBackend()
     T, H = q.shape[1], q.shape[2]
-    if pieces <= 0:
-        pieces = choose_pieces(T, H, rank == 0)
-    bounds = split_pieces(T, pieces)
+    bounds = plan_bounds(T, H, rank == 0) if pieces <= 0 else split_pieces(T, pieces)
     n = len(bounds) - 1
     need_map = [1] * n
     first = None
