@@ -260,7 +260,7 @@ def main(argv=None):
     ap.add_argument("--workload", default="serving", choices=["serving", "longctx"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
-    ap.add_argument("--pieces", type=int, default=0, help="longctx: pieces per rank (0 = chosen by a wave model)")
+    ap.add_argument("--pieces", type=int, default=0, help="longctx: equal pieces per rank (0 = boundaries planned by simulating the segment launch)")
     ap.add_argument("--equal-shards", action="store_true", help="longctx: equal token shards instead of cost-balanced ones")
     ap.add_argument("--longctx-tokens", type=int, default=131072, help="longctx: sequence length (smaller values for profiler captures)")
     args = ap.parse_args(argv)
