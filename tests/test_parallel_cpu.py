@@ -116,6 +116,14 @@ def test_split_pieces_and_head_slice():
         bal = max(parallel.segment_cost(t, 96, i == 0) for i, t in enumerate(sh))
         eq = max(parallel.segment_cost(131072 // world, 96, i == 0) for i in range(world))
         assert bal < eq
+    # planned piece boundaries: start at 0, end at T, strictly increasing, chunk-aligned inside; with H = 96 on 148
+    # SMs the first rank keeps a long plain piece next to shorter mapped ones, and the plan beats a single piece
+    for T, H, first in ((131072, 96, True), (131072, 96, False), (1000, 4, True), (40, 2, True), (33, 2, False), (1, 1, True), (32, 3, False)):
+        b = parallel.plan_bounds(T, H, first)
+        assert b[0] == 0 and b[-1] == T and all(x < y for x, y in zip(b[:-1], b[1:])) and all(x % 32 == 0 for x in b[:-1])
+    b = parallel.plan_bounds(131072, 96, True)
+    assert len(b) >= 3 and b[1] - b[0] > b[2] - b[1]
+    assert parallel.segment_cost(131072, 96, True) < 4096
     assert parallel.balanced_shards(1000, 1, 4) == [1000]
     sh = parallel.balanced_shards(1000, 3, 4)
     assert sum(sh) == 1000 and all(x % 32 == 0 for x in sh[:-1])
