@@ -21,7 +21,8 @@ def kda():
 
 
 @pytest.mark.parametrize("H,T,pieces,slow,kernel", [(4, 1000, 4, False, 0), (2, 2048, 3, True, 0), (8, 333, 8, False, 0),
-                                                    (4, 1000, 4, False, 1), (3, 97, 2, False, 0), (2, 40, 5, False, 0)])
+                                                    (4, 1000, 4, False, 1), (3, 97, 2, False, 0), (2, 40, 5, False, 0),
+                                                    (96, 4096, 0, False, 0), (5, 777, 0, True, 0)])   # 0: planned boundaries
 def test_context_parallel_single_gpu(kda, H, T, pieces, slow, kernel):
     from kda_b200 import parallel
     inputs = ko.make_inputs_raw(H, [T], 40 + H + pieces)
