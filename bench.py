@@ -173,6 +173,67 @@ def run_reference(args, lens):
     return 0
 
 
+def run_layouts(args, dev, kda_b200):
+    """configs[4]: ONE captured CUDA graph (token capacity 32768, H = 64, up to 512 sequences, pool of 1024 slots)
+    replayed over four batch layouts by rewriting cu_seqlens in place; trailing sequences are empty."""
+    import random
+    T, H, N_CAP, SLOTS = 32768, H_TOTAL, 512, 1024
+    gen = torch.Generator(device=dev).manual_seed(11)
+    q = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=dev), dim=-1).to(torch.bfloat16)
+    v = torch.randn(1, T, H, D, generator=gen, device=dev).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=dev) + 2.0)
+    beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=dev))
+    pool = torch.randn(SLOTS, H, D, D, generator=gen, device=dev) * 0.05
+    slots = torch.randperm(SLOTS, generator=torch.Generator().manual_seed(3))[:N_CAP].to(torch.int32).to(dev)
+    rng = random.Random(5)
+    mix, left = [], T
+    while left > 0:
+        n = min(left, rng.randint(1, 4096))
+        mix.append(n)
+        left -= n
+    layouts = {"1x32768": [T], "32x1024": [1024] * 32, "512x64": [64] * 512, f"mix of {len(mix)} (U[1,4096])": mix}
+
+    def cu_of(lens):
+        c = [0]
+        for n in lens:
+            c.append(c[-1] + n)
+        c += [T] * (N_CAP + 1 - len(c))
+        return torch.tensor(c, dtype=torch.int64, device=dev)
+
+    cu = cu_of(layouts["32x1024"])
+    launch = kda_b200.prepare_plain(q, k, v, g, beta, D ** -0.5, pool, False, cu, dynamic_layout=True, ssm_state_indices=slots)
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch()
+    res = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, lens in layouts.items():
+        cu.copy_(cu_of(lens))
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        if kda_b200.status_bits(launch) != 0 or kda_b200.kernel_error(launch) != 0:
+            raise SystemExit(f"bench: layout {name} reported a table or kernel error")
+        res[name] = {"ms": round(ms, 4), "tokens_per_s": T / (ms * 1e-3)}
+    print(json.dumps({"metric": "KDA prefill tokens/s (H=64,K=V=128, one CUDA graph over batch layouts)", "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic",
+                      "config": {"workload": "configs[4]: token capacity 32768, H=64, 512 sequence slots, pool of 1024 slots, "
+                                             "g=logsigmoid(N(2,1)); one captured graph, cu_seqlens rewritten in place"},
+                      "layouts": res}))
+    return 0
+
+
 def run_longctx(args, world, rank, dev, kda_b200):
     """configs[3]: one sequence of 131072 tokens, H = 96, slow decay g = logsigmoid(N(2,1)), zero initial state; the
     tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up."""
@@ -257,7 +318,7 @@ def main(argv=None):
     ap.add_argument("--e2e-groups", type=int, default=6, help="end-to-end arm: request groups whose copies and prefills overlap")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
-    ap.add_argument("--workload", default="serving", choices=["serving", "longctx"],
+    ap.add_argument("--workload", default="serving", choices=["serving", "longctx", "layouts"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
     ap.add_argument("--pieces", type=int, default=0, help="longctx: equal pieces per rank (0 = boundaries planned by simulating the segment launch)")
@@ -285,6 +346,10 @@ def main(argv=None):
 
     if args.workload == "longctx":
         return run_longctx(args, world, rank, dev, kda_b200)
+    if args.workload == "layouts":
+        if world > 1:
+            raise SystemExit("--workload layouts runs on one GPU")
+        return run_layouts(args, dev, kda_b200)
     assert H_TOTAL % world == 0
     H = H_TOTAL // world
     T, N = sum(lens), len(lens)
