@@ -234,6 +234,68 @@ def run_layouts(args, dev, kda_b200):
     return 0
 
 
+def run_headline(args, dev, kda_b200):
+    """The single-GPU cases the reference publishes latencies for (kda/b200/README.md:84-116), with its own front-end
+    (bf16 gate and beta logits, A_log, dt_bias, L2 norm in the kernel), each call captured in a CUDA graph and timed
+    with a cold L2 (a 256 MB buffer is rewritten before every replay), median of the timed replays."""
+    from kda_b200 import parallel
+    cases = [("H=64, 1x8192", 64, [8192], 0, 0.2394), ("H=64, 8x1024", 64, [1024] * 8, 0, 0.1767),
+             ("H=96, 1x8192", 96, [8192], 0, 0.3034), ("H=96, 8x1024", 96, [1024] * 8, 0, 0.2524),
+             ("H=16, 1x32768, pool + bf16 checkpoints / 64", 16, [32768], 64, 0.4510),
+             ("H=12, 1x32768, pool + bf16 checkpoints / 64", 12, [32768], 64, 0.3645)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, H, lens, every, ref_ms in cases:
+        T, N = sum(lens), len(lens)
+        gen = torch.Generator(device=dev).manual_seed(31 + H)
+        mk = lambda *shape: torch.randn(*shape, generator=gen, device=dev).to(torch.bfloat16)
+        q, k, v, g, beta = mk(1, T, H, D), mk(1, T, H, D), mk(1, T, H, D), mk(1, T, H, D), mk(1, T, H)
+        A_log = torch.zeros(H, device=dev)
+        dt_bias = torch.zeros(H * D, device=dev)
+        cu = torch.tensor([0, *torch.tensor(lens).cumsum(0).tolist()], dtype=torch.int64, device=dev)
+        init = torch.randn(N, H, D, D, generator=gen, device=dev) * 0.05
+        kw = {}
+        if every:
+            rows = sum(-(-n // every) for n in lens)
+            counts = [-(-n // every) for n in lens]
+            kw = dict(dynamic_layout=True, ssm_state_indices=torch.arange(N, dtype=torch.int32, device=dev),
+                      state_checkpoints=torch.zeros(rows, H, D, D, dtype=torch.bfloat16, device=dev),
+                      checkpoint_cu_starts=torch.tensor([0, *torch.tensor(counts).cumsum(0).tolist()], dtype=torch.int64, device=dev),
+                      checkpoint_every_n_tokens=every)
+        launch = kda_b200.prepare(q, k, v, g, beta, A_log, dt_bias, D ** -0.5, init, cu, **kw)
+        for _ in range(3):
+            launch()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch()
+
+        def timed(fn):
+            ts = []
+            for _ in range(max(5, args.steps)):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return sorted(ts)[len(ts) // 2]
+
+        entry = {"ms": round(timed(graph.replay), 4), "reference_ms": ref_ms}
+        if N == 1 and not every:
+            # one long sequence without a pool: the context-parallel call on one GPU cuts it into pieces that fill the SMs
+            be = parallel.CudaBackend()
+            fn = lambda: parallel.context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, D ** -0.5, init, backend=be)
+            fn()
+            entry["ms_context_parallel_call"] = round(timed(fn), 4)
+        entry["tokens_per_s"] = T / (min(entry["ms"], entry.get("ms_context_parallel_call", 1e9)) * 1e-3)
+        out[name] = entry
+    print(json.dumps({"metric": "latency of the reference's published single-GPU cases (raw front-end, cold L2, CUDA graph)",
+                      "unit": "ms", "n_gpus": 1, "higher_is_better": False, "data": "synthetic", "cases": out}))
+    return 0
+
+
 def run_longctx(args, world, rank, dev, kda_b200):
     """configs[3]: one sequence of 131072 tokens, H = 96, slow decay g = logsigmoid(N(2,1)), zero initial state; the
     tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up."""
@@ -318,7 +380,7 @@ def main(argv=None):
     ap.add_argument("--e2e-groups", type=int, default=6, help="end-to-end arm: request groups whose copies and prefills overlap")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
-    ap.add_argument("--workload", default="serving", choices=["serving", "longctx", "layouts"],
+    ap.add_argument("--workload", default="serving", choices=["serving", "longctx", "layouts", "headline"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
     ap.add_argument("--pieces", type=int, default=0, help="longctx: equal pieces per rank (0 = boundaries planned by simulating the segment launch)")
@@ -346,6 +408,10 @@ def main(argv=None):
 
     if args.workload == "longctx":
         return run_longctx(args, world, rank, dev, kda_b200)
+    if args.workload == "headline":
+        if world > 1:
+            raise SystemExit("--workload headline runs on one GPU")
+        return run_headline(args, dev, kda_b200)
     if args.workload == "layouts":
         if world > 1:
             raise SystemExit("--workload layouts runs on one GPU")
