@@ -218,6 +218,120 @@ class CudaBackend:
         return out
 
 
+def plan_cut(T, H, every, n_sms=148, max_pieces=24, task_overhead=3.0):
+    """Number of equal pieces (aligned to the checkpoint interval) for `prepare_cut_sequence`, or 1 when cutting does
+    not pay.  Cost of p pieces in chunk steps: pass 1 runs the plain chain on piece 0 and both chains on pieces
+    1..p-2 (the last piece's map is not needed), pass 2 runs every piece once from its true entering state."""
+    align = max(CHUNK, int(every or CHUNK))
+    nch = -(-T // CHUNK)
+    best_p, best = 1, _makespan([nch + task_overhead] * H, n_sms)
+    for p in range(2, max_pieces + 1):
+        L = -(-(-(-T // p)) // align) * align
+        pe = -(-T // L)
+        if pe < 2:
+            continue
+        c = L // CHUNK + task_overhead
+        cost = _makespan([c] * (H * (1 + 2 * max(0, pe - 2))), n_sms) + _makespan([c] * (H * pe), n_sms)
+        if cost < best * 0.9:
+            best_p, best = pe, cost
+    return best_p
+
+
+def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *, state_checkpoints=None, checkpoint_row0=0,
+                         checkpoint_every_n_tokens=0, pieces=0):
+    """Serving prefill of ONE long sequence on few heads, cut into pieces so that all SMs work, WITH checkpoint rows.
+
+    q, k, v, g [1, T, H, 128] bf16 and beta [1, T, H] bf16 (the reference front-end), pool [P, H, 128, 128] fp32
+    value-first updated in place at `slot`; `state_checkpoints` [C, H, 128, 128] (fp32 or bf16) receives the state
+    before every `checkpoint_every_n_tokens`-th token in rows `checkpoint_row0 ...`, exactly as the ordinary call.
+
+    Two passes, because checkpoint rows need true states: pass 1 gets every piece's entering state from the affine
+    maps (plain chain on piece 0, chains L and Tr on the middle pieces, nothing on the last) and one scan; pass 2 is the
+    ordinary serving launch over the pieces as if they were sequences, each starting from its entering state through
+    the source-pool arguments, emitting outputs and checkpoint rows.  Three piece-chains of work instead of one, on up
+    to 148 SMs instead of H (the reference cuts long requests inside its planner, kda/b200/csrc/w3/base/kernel.py:362-593).
+    Returns launch() -> (out [1, T, H, 128] bf16, pool, state_checkpoints); everything is allocated here, the launch
+    only enqueues kernels and device copies on the current stream (no host synchronisation)."""
+    import kda_b200
+    dev = q.device
+    T, H = q.shape[1], q.shape[2]
+    every = int(checkpoint_every_n_tokens or 0)
+    lib = _cabi.lib()
+    p = pieces if pieces > 0 else plan_cut(T, H, every)
+    align = max(CHUNK, every or CHUNK)
+    L = -(-(-(-T // max(p, 1))) // align) * align
+    p = -(-T // L)
+    ck_kw = {}
+    if every:
+        ck_kw = dict(state_checkpoints=state_checkpoints, checkpoint_every_n_tokens=every)
+    if p < 2:
+        starts = torch.tensor([checkpoint_row0, checkpoint_row0 + -(-T // every)], dtype=torch.int64, device=dev) if every else None
+        return kda_b200.prepare(q, k, v, g, beta, A_log, dt_bias, scale, pool, None, dynamic_layout=True,
+                                ssm_state_indices=torch.tensor([slot], dtype=torch.int32, device=dev),
+                                **(dict(ck_kw, checkpoint_cu_starts=starts) if every else {}))
+    bounds = [min(T, i * L) for i in range(p + 1)]
+    n1 = p - 1                                   # pieces whose end state pass 1 has to deliver
+    T1 = bounds[n1]
+    # ---- pass 1: maps of pieces 0 .. p-2
+    out1 = torch.empty(1, T1, H, D, dtype=torch.bfloat16, device=dev)
+    qt1 = torch.empty(1, T1, H, D, dtype=torch.bfloat16, device=dev)
+    P = torch.zeros(n1, H, D, D, dtype=torch.float32, device=dev)
+    S_loc = torch.empty(n1, H, D, D, dtype=torch.float32, device=dev)
+    t0 = torch.tensor(bounds[:n1], dtype=torch.int64, device=dev)
+    t1 = torch.tensor(bounds[1:n1 + 1], dtype=torch.int64, device=dev)
+    nm = torch.tensor([0] + [1] * (n1 - 1), dtype=torch.int32, device=dev)
+    ws_bytes = lib.kda_prefill_workspace_bytes(2 * n1, H)
+    ws = torch.zeros(ws_bytes + 256, dtype=torch.uint8, device=dev)
+    status1 = torch.zeros(4, dtype=torch.int32, device=dev)
+    first = pool[slot:slot + 1]
+    seg = _cabi.KdaSegmentArgs()
+    a = seg.base
+    a.q, a.k, a.v, a.g, a.beta, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), out1.data_ptr()
+    a.ldq, a.ldk, a.ldv, a.ldg = (t.stride(1) for t in (q, k, v, g))
+    a.ldbeta, a.ldo = beta.stride(1), H * D
+    a.A_log, a.dt_bias = A_log.data_ptr(), dt_bias.data_ptr()
+    a.scale, a.lower_bound = float(scale), -5.0
+    a.frontend, a.state_layout = _cabi.FRONTEND_RAW, _cabi.STATE_VALUE_FIRST
+    a.H, a.N, a.T = H, n1, T1
+    a.src_base, a.src_slot_stride, a.src_slots = first.data_ptr(), first.stride(0), 1
+    a.workspace, a.workspace_bytes = (ws.data_ptr() + 255) // 256 * 256, ws_bytes
+    a.status = status1.data_ptr()
+    a.kernel = kda_b200.default_kernel()
+    seg.n_seg = n1
+    seg.seg_t0, seg.seg_t1, seg.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
+    seg.qt, seg.P, seg.S_loc = qt1.data_ptr(), P.data_ptr(), S_loc.data_ptr()
+    # ---- scan: entering states of all p pieces, laid out as the source pool of pass 2
+    src = torch.empty(p, H, D, D, dtype=torch.float32, device=dev)
+    # ---- pass 2: the ordinary serving launch over the pieces
+    dstpool = torch.empty(p, H, D, D, dtype=torch.float32, device=dev)
+    ids = torch.arange(p, dtype=torch.int32, device=dev)
+    cu2 = torch.tensor(bounds, dtype=torch.int64, device=dev)
+    kw = dict(dynamic_layout=True, ssm_state_indices=ids, initial_state_source=src, initial_state_indices=ids)
+    if every:
+        rows = [0]
+        for i in range(p):
+            rows.append(rows[-1] + -(-(bounds[i + 1] - bounds[i]) // every))
+        kw.update(state_checkpoints=state_checkpoints, checkpoint_every_n_tokens=every,
+                  checkpoint_cu_starts=torch.tensor([checkpoint_row0 + r for r in rows], dtype=torch.int64, device=dev))
+    launch2 = kda_b200.prepare(q, k, v, g, beta, A_log, dt_bias, scale, dstpool, cu2, **kw)
+    keep = (out1, qt1, P, S_loc, t0, t1, nm, ws, status1, first, src, dstpool, ids, cu2)
+
+    def launch():
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _cabi.check(lib.kda_segment_launch(C.byref(seg), stream), "kda_segment_launch")
+        _cabi.check(lib.kda_scan_launch(P.data_ptr(), S_loc.data_ptr(), first.data_ptr(), src.data_ptr(),
+                                        src[n1].data_ptr(), n1, H, stream), "kda_scan_launch")
+        res = launch2()
+        pool[slot].copy_(dstpool[p - 1])
+        return (res[0], pool, state_checkpoints) if every else (res[0], pool)
+
+    launch.keepalive = keep
+    launch.pieces = p
+    launch.status = launch2.status
+    launch.status_pass1 = status1
+    return launch
+
+
 def compose_rank_map(backend, P, S_loc):
     """Total map of a rank's pieces per head: P_rank = P_0 @ P_1 @ ..., L_rank = (..(S_loc_0 @ P_1 + S_loc_1) @ P_2 ..)."""
     n = P.shape[0]

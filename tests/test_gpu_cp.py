@@ -73,3 +73,50 @@ def test_state_rows_copy(kda):
     assert lib.kda_state_rows_copy(dstb.data_ptr(), H * D * D, 1, src.data_ptr(), H * D * D, idx.data_ptr(), 3, H, st) == 0
     torch.cuda.synchronize()
     assert torch.equal(dstb, src[idx.long()].to(torch.bfloat16))       # round to nearest even
+
+
+@pytest.mark.parametrize("H,T,every,pieces,ck_dtype", [(4, 2048, 64, 4, torch.float32), (3, 1000, 64, 3, torch.bfloat16),
+                                                       (2, 4096, 0, 5, None), (16, 8192, 256, 0, torch.bfloat16)])
+def test_cut_sequence_matches_the_serving_call(kda, H, T, every, pieces, ck_dtype):
+    """One long sequence cut into pieces (two passes: affine maps + scan for the entering states, then the ordinary
+    launch over the pieces) gives the output, pool slot and checkpoint rows of the uncut serving call and of the fp64
+    recurrence."""
+    from kda_b200 import parallel
+    inputs = ko.make_inputs_raw(H, [T], 70 + H)
+    q, k, v, g, beta, A_log, dt_bias, scale, init, _ = to_dev(inputs)
+    gen = torch.Generator().manual_seed(5)
+    pool0 = (torch.randn(6, H, D, D, generator=gen) * 0.25).to(DEV)
+    slot, row0 = 4, 3
+    rows = -(-T // every) if every else 0
+    res = {}
+    for mode in ("plain", "cut"):
+        pool = pool0.clone()
+        ck = torch.full((rows + row0 + 2, H, D, D), float("nan"), dtype=ck_dtype, device=DEV) if every else None
+        if mode == "plain":
+            kw = dict(dynamic_layout=True, ssm_state_indices=torch.tensor([slot], dtype=torch.int32, device=DEV))
+            if every:
+                kw.update(state_checkpoints=ck, checkpoint_every_n_tokens=every,
+                          checkpoint_cu_starts=torch.tensor([row0, row0 + rows], dtype=torch.int64, device=DEV))
+            launch = kda.prepare(q, k, v, g, beta, A_log, dt_bias, scale, pool, None, **kw)
+        else:
+            launch = parallel.prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, state_checkpoints=ck,
+                                                   checkpoint_row0=row0, checkpoint_every_n_tokens=every, pieces=pieces)
+            assert launch.pieces >= 2
+        out = launch()[0]
+        launch()                                   # a second call on the updated pool must not depend on leftovers
+        pool.copy_(pool0)
+        out = launch()[0]
+        torch.cuda.synchronize()
+        assert kda.status_bits(launch) == 0 and kda.kernel_error(launch) == 0
+        res[mode] = (out.clone(), pool.clone(), None if ck is None else ck.clone())
+    gold_o, gold_s, gold_ck = gold_raw(inputs[:8] + [pool0[slot:slot + 1].cpu()], [T], every=every)
+    tag = f"cut sequence H={H} T={T} every={every} pieces={pieces}"
+    ko.check_close(res["cut"][0].cpu(), gold_o, tag + " output")
+    ko.check_close(res["cut"][1][slot].cpu(), gold_s[0], tag + " pool slot")
+    ko.check_close(res["cut"][0].cpu().float(), res["plain"][0].cpu().float(), tag + " output vs uncut call")
+    ko.check_close(res["cut"][1][slot].cpu(), res["plain"][1][slot].cpu(), tag + " pool slot vs uncut call")
+    others = [i for i in range(6) if i != slot]
+    assert torch.equal(res["cut"][1][others], pool0[others]), tag + ": other pool slots changed"
+    if every:
+        ko.check_close(res["cut"][2][row0:row0 + rows].float().cpu(), res["plain"][2][row0:row0 + rows].float().cpu(), tag + " checkpoint rows")
+        assert torch.isnan(res["cut"][2][:row0].float()).all() and torch.isnan(res["cut"][2][row0 + rows:].float()).all(), tag + ": rows outside the range written"
