@@ -201,7 +201,14 @@ int kda_prefill_launch_noalloc(const KdaPrefillArgs* a, void* stream_) {
 int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (s == nullptr) return KDA_ERR_ARG;
-  const KdaPrefillArgs* a = &s->base;
+  // qt == NULL: maps only (P, S_loc); neither chain writes output rows and `out` may be NULL as well
+  const bool maps_only = s->qt == nullptr;
+  KdaPrefillArgs base = s->base;
+  if (maps_only && base.out == nullptr) {
+    base.out = const_cast<void*>(base.q);      // never written in this mode; only here to pass the pointer checks
+    base.ldo = base.ldq;
+  }
+  const KdaPrefillArgs* a = &base;
   int rc = check_tokens(a);
   if (rc != KDA_OK) return rc;
   if (s->n_seg < 1 || !s->seg_t0 || !s->seg_t1 || !s->seg_need_map || !s->S_loc) return KDA_ERR_ARG;
@@ -213,6 +220,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   sp.t0 = reinterpret_cast<const long long*>(s->seg_t0); sp.t1 = reinterpret_cast<const long long*>(s->seg_t1);
   sp.need_map = s->seg_need_map;
   sp.src_base = a->src_base; sp.src_stride = a->src_slot_stride;
+  sp.no_out = maps_only ? 1 : 0;
   sp.P = s->P; sp.S_loc = s->S_loc;
   sp.tasks = w.tasks; sp.n_tasks = w.n_tasks; sp.status = a->status;
   cudaError_t e = kda::launch_seg_plan(sp, stream);

@@ -29,6 +29,10 @@ __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
       else l.flags = TF_INIT_ZERO;
       r.len = 0; r.flags = TF_INIT_ZERO | TF_NO_OUT; r.dst = nullptr;
     }
+    if (a.no_out) {
+      l.flags |= TF_NO_OUT;
+      r.flags |= TF_NO_OUT;
+    }
     a.tasks[2 * i] = l;
     a.tasks[2 * i + 1] = r;
   }

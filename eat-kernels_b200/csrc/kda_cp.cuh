@@ -11,6 +11,7 @@ struct SegPlanParams {
   const long long* t1;
   const int* need_map;
   const float* src_base; long long src_stride;
+  int no_out;      // maps only: neither chain writes output rows
   float* P;
   float* S_loc;
   Task* tasks;     // [2 * n_seg]

@@ -273,8 +273,6 @@ def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *,
     n1 = p - 1                                   # pieces whose end state pass 1 has to deliver
     T1 = bounds[n1]
     # ---- pass 1: maps of pieces 0 .. p-2
-    out1 = torch.empty(1, T1, H, D, dtype=torch.bfloat16, device=dev)
-    qt1 = torch.empty(1, T1, H, D, dtype=torch.bfloat16, device=dev)
     P = torch.zeros(n1, H, D, D, dtype=torch.float32, device=dev)
     S_loc = torch.empty(n1, H, D, D, dtype=torch.float32, device=dev)
     t0 = torch.tensor(bounds[:n1], dtype=torch.int64, device=dev)
@@ -286,7 +284,8 @@ def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *,
     first = pool[slot:slot + 1]
     seg = _cabi.KdaSegmentArgs()
     a = seg.base
-    a.q, a.k, a.v, a.g, a.beta, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), out1.data_ptr()
+    a.q, a.k, a.v, a.g, a.beta = q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr()
+    a.out = None                                 # maps only: pass 1 writes no output rows
     a.ldq, a.ldk, a.ldv, a.ldg = (t.stride(1) for t in (q, k, v, g))
     a.ldbeta, a.ldo = beta.stride(1), H * D
     a.A_log, a.dt_bias = A_log.data_ptr(), dt_bias.data_ptr()
@@ -299,7 +298,7 @@ def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *,
     a.kernel = kda_b200.default_kernel()
     seg.n_seg = n1
     seg.seg_t0, seg.seg_t1, seg.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
-    seg.qt, seg.P, seg.S_loc = qt1.data_ptr(), P.data_ptr(), S_loc.data_ptr()
+    seg.qt, seg.P, seg.S_loc = None, P.data_ptr(), S_loc.data_ptr()
     # ---- scan: entering states of all p pieces, laid out as the source pool of pass 2
     src = torch.empty(p, H, D, D, dtype=torch.float32, device=dev)
     # ---- pass 2: the ordinary serving launch over the pieces
@@ -314,7 +313,7 @@ def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *,
         kw.update(state_checkpoints=state_checkpoints, checkpoint_every_n_tokens=every,
                   checkpoint_cu_starts=torch.tensor([checkpoint_row0 + r for r in rows], dtype=torch.int64, device=dev))
     launch2 = kda_b200.prepare(q, k, v, g, beta, A_log, dt_bias, scale, dstpool, cu2, **kw)
-    keep = (out1, qt1, P, S_loc, t0, t1, nm, ws, status1, first, src, dstpool, ids, cu2)
+    keep = (P, S_loc, t0, t1, nm, ws, status1, first, src, dstpool, ids, cu2)
 
     def launch():
         stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)

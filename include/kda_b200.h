@@ -153,7 +153,8 @@ typedef struct KdaSegmentArgs {
   const int64_t* seg_t0;      /* device [n_seg] */
   const int64_t* seg_t1;      /* device [n_seg] */
   const int32_t* seg_need_map;/* device [n_seg] */
-  void* qt;                   /* bf16 [T][H][128] (ldo stride): Qt rows of mapped segments */
+  void* qt;                   /* bf16 [T][H][128] (ldo stride): Qt rows of mapped segments; NULL = maps only: no output
+                                 rows are written by either chain and base.out may be NULL too */
   float* P;                   /* [n_seg][H][128][128] transition maps, value-first */
   float* S_loc;               /* [n_seg][H][128][128] offsets; for unmapped segments the true end state */
 } KdaSegmentArgs;
