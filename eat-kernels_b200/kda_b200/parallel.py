@@ -152,6 +152,19 @@ class CudaBackend:
         from . import default_kernel
         self.lib = _cabi.lib()
         self.kernel = default_kernel() if kernel is None else int(kernel)
+        self._table_cache = {}
+
+    def _tables(self, bounds, need_map, dev):
+        """Device copies of the piece tables, kept per layout: a repeated call uploads nothing."""
+        key = (tuple(bounds), tuple(need_map), str(dev))
+        t = self._table_cache.get(key)
+        if t is None:
+            if len(self._table_cache) > 64:
+                self._table_cache.clear()
+            t = (torch.tensor(bounds[:-1], dtype=torch.int64, device=dev), torch.tensor(bounds[1:], dtype=torch.int64, device=dev),
+                 torch.tensor(need_map, dtype=torch.int32, device=dev))
+            self._table_cache[key] = t
+        return t
 
     @staticmethod
     def _stream(dev):
@@ -167,9 +180,7 @@ class CudaBackend:
         qt = torch.empty(1, T, H, D, dtype=torch.bfloat16, device=dev)
         P = torch.zeros(n, H, D, D, dtype=torch.float32, device=dev)
         S_loc = torch.empty(n, H, D, D, dtype=torch.float32, device=dev)
-        t0 = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
-        t1 = torch.tensor(bounds[1:], dtype=torch.int64, device=dev)
-        nm = torch.tensor(need_map, dtype=torch.int32, device=dev)
+        t0, t1, nm = self._tables(bounds, need_map, dev)
         ws_bytes = self.lib.kda_prefill_workspace_bytes(2 * n, H)
         ws = torch.zeros(ws_bytes + 256, dtype=torch.uint8, device=dev)
         status = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -209,9 +220,7 @@ class CudaBackend:
     def fixup(self, out, qt, S_in, bounds, need_map):
         dev = out.device
         n, H = len(bounds) - 1, out.shape[2]
-        t0 = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
-        t1 = torch.tensor(bounds[1:], dtype=torch.int64, device=dev)
-        nm = torch.tensor(need_map, dtype=torch.int32, device=dev)
+        t0, t1, nm = self._tables(bounds, need_map, dev)
         _cabi.check(self.lib.kda_fixup_launch(out.data_ptr(), qt.data_ptr(), H * D, S_in.data_ptr(), t0.data_ptr(), t1.data_ptr(),
                                               nm.data_ptr(), n, H, self._stream(dev)), "kda_fixup_launch")
         self._keep2 = (t0, t1, nm)
@@ -375,6 +384,15 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     out, qt, P, S_loc = backend.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first)
     mark("segments")
     # P of an unmapped piece is the zero map (its S_loc is the true end state): segment_maps leaves it zero-filled
+    if world == 1:
+        # one rank: a single scan yields both the entering states of the pieces and the final state
+        mark("maps")
+        mark("exchange")
+        S_in, S_final = backend.scan(P, S_loc, None)
+        mark("scan")
+        out = backend.fixup(out, qt, S_in, bounds, need_map)
+        mark("fixup")
+        return out, S_final[None]
     P_rank, L_rank = compose_rank_map(backend, P, S_loc)
     mark("maps")
     if world > 1:
