@@ -16,6 +16,11 @@ int cuda_fail(cudaError_t e) {
   return KDA_ERR_LAUNCH;
 }
 
+// Diagnostic configuration (kda_debug_configure): process-wide, meant for tests and profiling runs only.
+unsigned long long g_wait_limit_ns = 0;
+int g_debug_flags = 0;
+unsigned long long* g_prof = nullptr;
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -81,14 +86,39 @@ void fill_chunk_params(kda::ChunkParams& p, const KdaPrefillArgs* a) {
   p.H = a->H;
   p.T = a->T;
   p.status = a->status;
+  p.wait_limit_ns = g_wait_limit_ns;
+  p.debug_flags = g_debug_flags;
+  p.prof = g_prof;
 }
 
 // Tensor maps of the token tensors for the tcgen05 kernel's copy engine (q, k, v in 64-channel halves with the 128-byte
 // swizzle, g as whole 128-channel rows).  T == 0: nothing is ever copied, the maps stay zeroed.
+// A prepared launch calls with the same pointers and strides every time, so the encoded maps are kept per thread
+// (a few entries, replaced round-robin) instead of going through the driver's encoder at every launch.
+struct MapKey {
+  const void *q, *k, *v, *g;
+  int64_t ldq, ldk, ldv, ldg, T;
+  int32_t H, frontend;
+  bool operator==(const MapKey& o) const {
+    return q == o.q && k == o.k && v == o.v && g == o.g && ldq == o.ldq && ldk == o.ldk && ldv == o.ldv && ldg == o.ldg &&
+           T == o.T && H == o.H && frontend == o.frontend;
+  }
+};
+constexpr int kMapCache = 16;
+thread_local MapKey g_map_keys[kMapCache];
+thread_local kda::TmaMaps g_map_vals[kMapCache];
+thread_local int g_map_used = 0, g_map_next = 0;
+
 int fill_tma_maps(kda::TmaMaps& m, const KdaPrefillArgs* a) {
   memset(&m, 0, sizeof(m));
   if (a->T <= 0) return KDA_OK;
   if (a->T > 0x7fffffffLL) return KDA_ERR_LIMIT;
+  const MapKey key = {a->q, a->k, a->v, a->g, a->ldq, a->ldk, a->ldv, a->ldg, a->T, a->H, a->frontend};
+  for (int i = 0; i < g_map_used; i++)
+    if (g_map_keys[i] == key) {
+      m = g_map_vals[i];
+      return KDA_OK;
+    }
   const bool plain = a->frontend == KDA_FRONTEND_PLAIN;
   int rc = kda::encode_token_map(&m.q, a->q, 2, false, a->T, a->H, a->ldq, 64, true);
   if (rc == 0) rc = kda::encode_token_map(&m.k, a->k, 2, false, a->T, a->H, a->ldk, 64, true);
@@ -98,6 +128,9 @@ int fill_tma_maps(kda::TmaMaps& m, const KdaPrefillArgs* a) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (%d)", rc);
     return KDA_ERR_LAUNCH;
   }
+  const int slot = g_map_used < kMapCache ? g_map_used++ : (g_map_next++ % kMapCache);
+  g_map_keys[slot] = key;
+  g_map_vals[slot] = m;
   return KDA_OK;
 }
 
@@ -172,6 +205,8 @@ constexpr size_t kNoallocBytes = 2 * 12288 /* task tables, 64 x 48 B each rounde
                                  1024 /* cu_seqlens copy */ + (size_t)KDA_NOALLOC_MAX_HEADS * kda::STATE_ELEMS * sizeof(float) + 4096;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocBytes];
 constexpr int kMaxDevices = 64;
+// Filled without a lock: two threads racing on a device's first call both look the same address up and store the same
+// value, so the race is benign.
 void* g_noalloc_addr[kMaxDevices] = {};
 }  // namespace
 
@@ -283,6 +318,14 @@ const char* kda_error_string(int code) {
 
 size_t kda_abi_struct_bytes(int which) { return which == 0 ? sizeof(KdaPrefillArgs) : (which == 1 ? sizeof(KdaSegmentArgs) : 0); }
 
-const char* kda_version(void) { return "kda_b200 1 sm_100a"; }
+const char* kda_version(void) { return "kda_b200 2 sm_100a"; }
+
+int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters) {
+  if (wait_limit_us < 0 || (flags & ~kda::DBG_SKIP_V_STREAM)) return KDA_ERR_ARG;
+  g_wait_limit_ns = (unsigned long long)wait_limit_us * 1000ull;
+  g_debug_flags = flags;
+  g_prof = reinterpret_cast<unsigned long long*>(prof_counters);
+  return KDA_OK;
+}
 
 }  // extern "C"

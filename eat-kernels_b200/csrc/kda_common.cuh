@@ -52,7 +52,13 @@ struct ChunkParams {
   const int* n_tasks;  // device: number of valid tasks
   int* status;         // device int[4]
   long long T;         // token rows (for the zero-fill of a rejected layout)
+  unsigned long long wait_limit_ns;   // bound of every in-kernel wait (0 = the built-in default)
+  int debug_flags;     // DBG_* below; 0 in every product launch
+  unsigned long long* prof;           // cycle counters of profiling builds (KDA_PROF), else unused
 };
+
+// Diagnostic switches of the tcgen05 kernel (set only through kda_debug_configure).
+constexpr int DBG_SKIP_V_STREAM = 1;   // the loader never issues the v copies: a waiter runs into its bound
 
 // ----------------------------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

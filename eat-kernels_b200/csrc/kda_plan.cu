@@ -9,7 +9,9 @@
 //   bit 1  cu_seqlens not 0-based / decreasing / beyond T: every sequence becomes empty
 //   bit 2  destination slot out of range or already claimed by an earlier sequence: final state goes to scratch
 //   bit 4  source slot out of range: the sequence starts from zeros
-//   bit 8  checkpoint rows out of range or overlapping an earlier sequence's rows: the sequence writes none
+//   bit 8  checkpoint rows out of range or overlapping the rows an earlier sequence KEEPS: the sequence writes none.
+//          Overlaps are resolved in ascending sequence order against final decisions, as the reference does
+//          (kda/b200/csrc/w3/validate_dev.cuh:124-142): a sequence that lost its rows does not block later ones.
 #include "kda_common.cuh"
 #include "kda_plan.cuh"
 
@@ -24,10 +26,18 @@ __device__ __forceinline__ long long rd_table(const void* p, int is64, long long
 
 __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanParams a) {
   __shared__ unsigned long long keys[SORT_MAX];
-  __shared__ int s_bits;
+  __shared__ unsigned char s_keep[SORT_MAX];     // checkpoint rows of sequence i: 0 = none / rejected, 1 = kept
+  __shared__ int s_bits, s_overlap;
   const int tid = threadIdx.x, bd = blockDim.x, N = a.N;
-  if (tid == 0) s_bits = 0;
+  if (tid == 0) { s_bits = 0; s_overlap = 0; }
   __syncthreads();
+  // rows [v, v + cnt) of sequence i and whether they lie inside the checkpoint buffer
+  auto ck_range = [&](int i, long long& v, long long& cnt) -> bool {
+    const long long len = a.cu_safe[i + 1] - a.cu_safe[i];
+    cnt = (len + a.ck_every - 1) / a.ck_every;
+    v = (a.ck_starts != nullptr) ? rd_table(a.ck_starts, a.ck_is64, i) : -1;
+    return v >= 0 && cnt <= a.ck_rows && v <= a.ck_rows - cnt;
+  };
 
   // ---- cu_seqlens
   bool cu_ok = true;
@@ -72,22 +82,19 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
       s = i;
       s_ok = true;
     }
-    // checkpoint rows
+    // checkpoint rows: range check here; overlaps with earlier sequences are only detected (resolved below)
     long long row = -1;
     if (a.ck_base != nullptr && a.ck_every > 0) {
-      const long long cnt = (len + a.ck_every - 1) / a.ck_every;
-      const long long v = (a.ck_starts != nullptr) ? rd_table(a.ck_starts, a.ck_is64, i) : -1;
-      bool ok = v >= 0 && cnt <= a.ck_rows && v <= a.ck_rows - cnt;
+      long long v, cnt;
+      bool ok = ck_range(i, v, cnt);
+      if (!ok) atomicOr(&s_bits, KDA_BIT_CKPT);
       if (ok && cnt > 0) {
-        for (int j = 0; j < i && ok; j++) {
-          const long long lj = a.cu_safe[j + 1] - a.cu_safe[j];
-          const long long cj = (lj + a.ck_every - 1) / a.ck_every;
-          const long long vj = rd_table(a.ck_starts, a.ck_is64, j);
-          const bool okj = vj >= 0 && cj <= a.ck_rows && vj <= a.ck_rows - cj;
-          if (okj && cj > 0 && vj < v + cnt && v < vj + cj) ok = false;
+        for (int j = 0; j < i; j++) {
+          long long vj, cj;
+          if (ck_range(j, vj, cj) && cj > 0 && vj < v + cnt && v < vj + cj) { s_overlap = 1; break; }
         }
       }
-      if (!ok) atomicOr(&s_bits, KDA_BIT_CKPT);
+      if (i < SORT_MAX) s_keep[i] = ok ? 1 : 0;
       row = ok ? v : -1;
     }
     Task t;
@@ -109,6 +116,30 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
                           : (void*)(reinterpret_cast<float*>(a.ck_base) + row * a.ck_row_stride);
     t.pad_ = 0;
     a.tasks_unsorted[i] = t;
+  }
+  __syncthreads();
+  if (s_overlap) {
+    // Malformed table (rare): one thread walks the sequences in order and drops the rows of every sequence that
+    // overlaps rows an EARLIER sequence keeps.  Beyond SORT_MAX sequences the flags do not fit: then every sequence
+    // that overlaps any earlier in-range sequence loses its rows (stricter, still race-free).
+    if (tid == 0) {
+      atomicOr(&s_bits, KDA_BIT_CKPT);
+      for (int i = 0; i < N; i++) {
+        long long v, cnt;
+        if (!ck_range(i, v, cnt) || cnt == 0) continue;
+        bool ok = true;
+        for (int j = 0; j < i && ok; j++) {
+          long long vj, cj;
+          if (!ck_range(j, vj, cj) || cj == 0) continue;
+          if ((N > SORT_MAX || s_keep[j]) && vj < v + cnt && v < vj + cj) ok = false;
+        }
+        if (!ok) {
+          if (i < SORT_MAX) s_keep[i] = 0;
+          a.tasks_unsorted[i].ck = nullptr;
+        }
+      }
+    }
+    __syncthreads();
   }
 
   // ---- order: longest first, ties by index (bitonic sort of (len descending, index) keys)

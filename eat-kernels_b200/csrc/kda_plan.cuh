@@ -5,7 +5,7 @@
 
 namespace kda {
 
-constexpr int KDA_BIT_CU = 1, KDA_BIT_SLOT = 2, KDA_BIT_SOURCE = 4, KDA_BIT_CKPT = 8;
+constexpr int KDA_BIT_CU = 1, KDA_BIT_SLOT = 2, KDA_BIT_SOURCE = 4, KDA_BIT_CKPT = 8, KDA_BIT_RANGE = 16;
 
 struct PlanParams {
   int N, H;

@@ -11,9 +11,10 @@
 //                       (16-bit operands; 32-bit MN-major operands need the 32-byte-base variant, see
 //                       mnmajor_f32_off.)
 //     Tiles are 1024-byte aligned so that the address-bit swizzle of the hardware equals the (row % 8) rule above.
-//   * Every wait on an mbarrier is bounded: after `kWaitLimitNs` of wall time the waiter raises the CTA's abort flag
-//     and carries on as if the wait had succeeded, so control flow (and every barrier count) stays intact, the kernel
-//     drains, frees its tensor memory and returns; the host reads the error code from the status word.
+//   * Every wait on an mbarrier is bounded: after `limit_ns` of wall time (kWaitLimitNs unless the launch overrides it)
+//     the waiter raises the CTA's abort flag and carries on as if the wait had succeeded, so control flow (and every
+//     barrier count) stays intact, the kernel drains, frees its tensor memory and returns; the host reads the error
+//     code from the status word.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -30,10 +31,12 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" :: "r"(bar) : "memory");
 }
+// Potentially blocking test: the hardware may suspend the thread until the phase completes or a time limit of its own
+// passes, so a waiting warp does not take issue slots from the warps it is waiting for.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(4000u) : "memory");
   return ok != 0;
 }
 // non-blocking test of a phase (never suspends the thread)
@@ -53,16 +56,21 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // waiter sleep between polls so that it does not take issue slots from the warps it is waiting for.
 // The polling loop is kept out of line: it is instantiated at dozens of wait sites, and instruction-cache footprint is
 // what limits the role-specialised kernels.
+// `abort_flag` points at the CTA's control words in shared memory: [0] abort code, [2..3] the wait limit in ns (64 bit).
+__device__ __forceinline__ unsigned long long wait_limit_of(volatile int* abort_flag) {
+  return *reinterpret_cast<volatile unsigned long long*>(abort_flag + 2);
+}
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, unsigned sleep_ns) {
+  const unsigned long long limit_ns = wait_limit_of(abort_flag);
   unsigned long long t0 = 0;
   uint32_t n = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (sleep_ns) __nanosleep(sleep_ns);
     if (*abort_flag != 0) return false;
-    if ((++n & 255u) == 0) {
+    if ((++n & 63u) == 0) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         atomicCAS(const_cast<int*>(abort_flag), 0, code);
         return false;
       }
@@ -73,6 +81,23 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, unsigned sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, code, sleep_ns);
+}
+// Bounded wait that does NOT return early when the CTA has already given up elsewhere: used before a CTA leaves, for
+// asynchronous work (bulk copies, tensor-core instructions) that must not be left in flight.  Returns false when the
+// limit ran out (the caller records the code; nothing more can be done).
+__device__ __noinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned long long limit_ns = wait_limit_of(abort_flag);
+  unsigned long long t0 = 0;
+  uint32_t n = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(64);
+    if ((++n & 63u) == 0) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
+    }
+  }
+  return true;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operand reads)
@@ -177,6 +202,128 @@ __device__ __forceinline__ void mma_ts_tf32_pred(uint32_t d_tmem, uint32_t a_tme
 __device__ __forceinline__ void mma_commit_pred(uint32_t bar, uint32_t go) {
   asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n"
                " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" :: "r"(bar), "r"(go) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------- MMA groups
+// A group of consecutive MMAs of one product as ONE block of PTX: the issue predicate is formed once, the accumulate
+// flags are constants, and each step only adds a literal to the low word of a descriptor (the start-address field is
+// the low 14 bits; no carry can leave it for addresses inside shared memory) and to a tensor-memory column.  The
+// issuing warp shares its scheduler with six others, so every instruction saved per MMA shortens the per-chunk chain.
+// Descriptors are passed as (low word, high word).
+// MMA1: 16 tf32 steps of K = 8; A = 8 state columns per step, B = [kd ; qd] (K-major, 32-channel blocks 8192 bytes apart)
+__device__ __forceinline__ void mma1_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
+  asm volatile(
+      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
+      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
+      " setp.ne.b32 p0, %5, %5;\n"
+      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
+      " add.u32 lo, %2, 2;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 4;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 6;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 512;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 32;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 514;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 40;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 516;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 48;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 518;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 56;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1024;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 64;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1026;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 72;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1028;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 80;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1030;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 88;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1536;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 96;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1538;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 104;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1540;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 112;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 1542;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 120;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      "}\n"
+      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
+}
+
+// four tf32 steps of K = 8 over a K-major B tile of one 128-byte row block (Tb, M); the first step overwrites unless acc_first
+__device__ __forceinline__ void mma_ts4_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go, uint32_t acc_first) {
+  asm volatile(
+      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
+      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
+      " setp.ne.b32 p0, %6, 0;\n"
+      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
+      " add.u32 lo, %2, 2;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 4;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 6;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      "}\n"
+      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go), "r"(acc_first) : "memory");
+}
+
+// MMA3 state part: four tf32 steps of K = 8 over the MN-major kr tile (4096 bytes per step)
+__device__ __forceinline__ void mma3s_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go, uint32_t acc_first) {
+  asm volatile(
+      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
+      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
+      " setp.ne.b32 p0, %6, 0;\n"
+      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
+      " add.u32 lo, %2, 256;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 512;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      " add.u32 lo, %2, 768;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
+      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
+      "}\n"
+      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go), "r"(acc_first) : "memory");
+}
+
+// MMA2 first part: two bf16 steps of K = 16, A = v tile (MN-major, 2048 bytes per step), B = bf16 Tb (64-byte rows)
+__device__ __forceinline__ void mma2a_block(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
+  asm volatile(
+      "{\n .reg .pred q, pt, p0;\n .reg .b32 la, lb;\n .reg .b64 da, db;\n"
+      " setp.ne.b32 q, %6, 0;\n setp.eq.b32 pt, %6, %6;\n setp.ne.b32 p0, %6, %6;\n"
+      " add.u32 la, %1, 0;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 0;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p0;\n"
+      " add.u32 la, %1, 128;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 2;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      "}\n"
+      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
+}
+
+// MMA0: eight bf16 steps of K = 16, A = interleaved q / k tiles (64-channel halves 8192 bytes apart), B = ki' (halves 4096 apart)
+__device__ __forceinline__ void mma0_block(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
+  asm volatile(
+      "{\n .reg .pred q, pt, p0;\n .reg .b32 la, lb;\n .reg .b64 da, db;\n"
+      " setp.ne.b32 q, %6, 0;\n setp.eq.b32 pt, %6, %6;\n setp.ne.b32 p0, %6, %6;\n"
+      " add.u32 la, %1, 0;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 0;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p0;\n"
+      " add.u32 la, %1, 2;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 2;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 4;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 4;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 6;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 6;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 512;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 256;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 514;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 258;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 516;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 260;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      " add.u32 la, %1, 518;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 262;\n mov.b64 db, {lb, %4};\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
+      "}\n"
+      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------- tile addressing

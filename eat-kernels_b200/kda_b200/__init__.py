@@ -45,37 +45,49 @@ def _err(msg):
     return ValueError("KDA kernel: " + msg)
 
 
-def _span(t):
-    if t is None or t.numel() == 0:
+def _byte_interval(t):
+    """[lo, hi) of the bytes a tensor's elements can touch (its extreme elements under its strides), or None when empty."""
+    if t is None or not torch.is_tensor(t) or t.numel() == 0:
         return None
-    lo = t.data_ptr()
-    return lo, lo + (sum((n - 1) * abs(s) for n, s in zip(t.shape, t.stride())) + 1) * t.element_size()
+    reach = 0
+    for extent, stride in zip(t.shape, t.stride()):
+        reach += (extent - 1) * abs(stride)
+    return t.data_ptr(), t.data_ptr() + (reach + 1) * t.element_size()
 
 
-def _check_overlap(written, read_only):
-    """A written buffer (state pool, checkpoint buffer) must not share memory with any other operand: the result would
-    depend on the order sequences are processed in (kda/b200/csrc/w3/kernel.py:1016-1026)."""
-    spans = [(n, _span(t)) for n, t in written]
-    for i, (n, sp) in enumerate(spans):
-        if sp is None:
-            continue
-        for m, so in [(m, _span(t)) for m, t in read_only] + spans[:i] + spans[i + 1:]:
-            if so is not None and sp[0] < so[1] and so[0] < sp[1]:
-                raise _err(f"{n} overlaps the memory of {m}: written buffers must not alias any other operand")
+def _reject_aliasing(written, read_only):
+    """Buffers the launch writes (state pool, checkpoint rows) may not share bytes with one another or with anything it
+    reads: sequences are processed in an order the caller does not control, so the result would depend on it.  The
+    reference refuses such calls as well (kda/b200/csrc/w3/kernel.py:1016-1026).  One sweep over the intervals sorted by
+    start address: an overlap exists exactly when some interval starts before the furthest end seen so far."""
+    ivs = []
+    for is_written, group in ((True, written), (False, read_only)):
+        for name, t in group:
+            iv = _byte_interval(t)
+            if iv is not None:
+                ivs.append((iv[0], iv[1], is_written, name))
+    ivs.sort(key=lambda r: r[0])
+    # furthest-reaching written and read-only interval seen so far: (end, name)
+    far = {True: (0, None), False: (0, None)}
+    for lo, hi, is_written, name in ivs:
+        clash = far[True] if far[True][0] > lo else (far[False] if is_written and far[False][0] > lo else None)
+        if clash is not None:
+            w, o = (name, clash[1]) if is_written else (clash[1], name)
+            raise _err(f"{w} overlaps the memory of {o}: written buffers must not alias any other operand")
+        if hi > far[is_written][0]:
+            far[is_written] = (hi, name)
 
 
 def _token_view_ok(t, width):
-    """True when the kernel can read `t` ([1,T,H,width] or [1,T,H]) in place: unit inner stride, heads `width` apart,
-    token stride a multiple of 8 elements, 16-byte aligned base."""
-    if t.dim() == 4:
-        ok = t.stride(3) == 1 and (t.shape[2] == 1 or t.stride(2) == width)
-        ld = t.stride(1)
-    else:
-        ok = t.shape[2] == 1 or t.stride(2) == 1
-        ld = t.stride(1)
-    if t.shape[1] <= 1:
-        return ok and t.data_ptr() % 16 == 0
-    return ok and ld % 8 == 0 and ld >= t.shape[2] * (width if t.dim() == 4 else 1) and t.data_ptr() % 16 == 0
+    """True when the kernel can read `t` in place.  [1,T,H,width] tiles go through the copy engine: unit inner stride,
+    heads `width` apart, token stride a multiple of 8 elements, 16-byte aligned base.  beta [1,T,H] is read with scalar
+    loads: unit head stride and a token stride of at least H are enough (any H, any alignment)."""
+    T, H = t.shape[1], t.shape[2]
+    if t.dim() == 3:
+        return (H == 1 or t.stride(2) == 1) and (T <= 1 or t.stride(1) >= H)
+    if t.stride(3) != 1 or (H > 1 and t.stride(2) != width) or t.data_ptr() % 16:
+        return False
+    return T <= 1 or (t.stride(1) % 8 == 0 and t.stride(1) >= H * width)
 
 
 def _table(t, name, n, live):
@@ -92,40 +104,44 @@ def _table(t, name, n, live):
 
 
 def _check_args(q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens, dynamic_layout, raw):
-    """Argument contract of kda/b200/csrc/w3/kernel.py:1255-1281."""
-    names = [("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta)]
+    """Shape / dtype / device contract of the call (the conditions of kda/b200/csrc/w3/kernel.py:1255-1281; a violation
+    raises ValueError).  Returns cu_seqlens, moved to q's device when the static path allows that."""
+    operands = {"q": q, "k": k, "v": v, "g": g, "beta": beta}
     if raw:
-        names += [("A_log", A_log), ("dt_bias", dt_bias)]
-    for name, t in names:
-        if not torch.is_tensor(t) or not t.is_cuda:
-            raise _err(f"{name} must be a CUDA tensor")
+        operands.update(A_log=A_log, dt_bias=dt_bias)
+    bad = [n for n, t in operands.items() if not (torch.is_tensor(t) and t.is_cuda)]
+    if bad:
+        raise _err(f"{bad[0]} must be a CUDA tensor")
     if q.dim() != 4 or q.shape[0] != 1 or q.shape[3] != D:
         raise _err(f"expected q of shape [1, T, H, 128], got {tuple(q.shape)}")
-    T, H = q.shape[1], q.shape[2]
-    for name, t in (("k", k), ("v", v), ("g", g)):
-        if tuple(t.shape) != tuple(q.shape):
-            raise _err(f"{name} must have the shape of q {tuple(q.shape)}, got {tuple(t.shape)}")
-    if beta.dim() < 2 or beta.shape[0] != 1 or beta.shape[1] != T or beta.numel() != T * H:
-        raise _err(f"beta must be [1, T, H] = [1, {T}, {H}], got {tuple(beta.shape)}")
-    if raw and (A_log.numel() != H or dt_bias.numel() != H * D):
-        raise _err(f"A_log must have H = {H} entries and dt_bias H * 128 = {H * D}, got {A_log.numel()} and {dt_bias.numel()}")
+    _, T, H, _ = q.shape
+    # (name, tensor, what it must look like, does it?)
+    rules = [(n, operands[n], f"the shape of q {tuple(q.shape)}", tuple(operands[n].shape) == tuple(q.shape)) for n in "kvg"]
+    rules.append(("beta", beta, f"[1, T, H] = [1, {T}, {H}]",
+                  beta.dim() >= 2 and beta.shape[0] == 1 and beta.shape[1] == T and beta.numel() == T * H))
+    if raw:
+        rules.append(("A_log", A_log, f"H = {H} entries", A_log.numel() == H))
+        rules.append(("dt_bias", dt_bias, f"H * 128 = {H * D} entries", dt_bias.numel() == H * D))
+    for name, t, want, ok in rules:
+        if not ok:
+            raise _err(f"{name} must have {want}, got {tuple(t.shape)}")
     if initial_state is not None and initial_state.dtype != torch.float32:
         raise _err(f"initial_state / the state pool must be fp32, got {initial_state.dtype}")
-    dev = q.device
-    for t in (k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens):
-        if torch.is_tensor(t) and t.is_cuda and t.device != dev:
-            raise _err(f"all CUDA tensors must be on the device of q ({dev}), got one on {t.device}")
-    if cu_seqlens is not None:
-        if not torch.is_tensor(cu_seqlens) or cu_seqlens.dim() != 1 or cu_seqlens.dtype not in (torch.int32, torch.int64):
-            raise _err("cu_seqlens must be a 1-D int32 / int64 tensor")
-        if cu_seqlens.numel() < 2:
-            raise _err("cu_seqlens must describe at least one sequence")
-        if cu_seqlens.device != dev or not cu_seqlens.is_contiguous():
-            if dynamic_layout:
-                raise _err("cu_seqlens must be a contiguous tensor on q's device with dynamic_layout=True "
-                           "(it is read in place at every replay)")
-            cu_seqlens = cu_seqlens.to(dev).contiguous()
-    return cu_seqlens
+    for t in (*operands.values(), initial_state, cu_seqlens):
+        if torch.is_tensor(t) and t.is_cuda and t.device != q.device:
+            raise _err(f"all CUDA tensors must be on the device of q ({q.device}), got one on {t.device}")
+    if cu_seqlens is None:
+        return None
+    if not (torch.is_tensor(cu_seqlens) and cu_seqlens.dim() == 1 and cu_seqlens.dtype in (torch.int32, torch.int64)):
+        raise _err("cu_seqlens must be a 1-D int32 / int64 tensor")
+    if cu_seqlens.numel() < 2:
+        raise _err("cu_seqlens must describe at least one sequence")
+    if cu_seqlens.device == q.device and cu_seqlens.is_contiguous():
+        return cu_seqlens
+    if dynamic_layout:
+        raise _err("cu_seqlens must be a contiguous tensor on q's device with dynamic_layout=True "
+                   "(it is read in place at every replay)")
+    return cu_seqlens.to(q.device).contiguous()
 
 
 class _Launch:
@@ -206,11 +222,11 @@ def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens,
         A_ = dtb_ = None
 
     # ---- state
-    _check_overlap([("the state pool", initial_state if pool else None),
-                    ("state_checkpoints", state_checkpoints if every else None)],
-                   [("initial_state_source", initial_state_source), ("initial_state", None if pool else initial_state)]
-                   + [(n, t) for n, t in zip("q k v g beta A_log dt_bias".split(), (q, k, v, g, beta, A_log, dt_bias))
-                      if torch.is_tensor(t)])
+    _reject_aliasing([("the state pool", initial_state if pool else None),
+                      ("state_checkpoints", state_checkpoints if every else None)],
+                     [("initial_state_source", initial_state_source), ("initial_state", None if pool else initial_state)]
+                     + [(n, t) for n, t in zip("q k v g beta A_log dt_bias".split(), (q, k, v, g, beta, A_log, dt_bias))
+                        if torch.is_tensor(t)])
     if initial_state is None and pool:
         raise _err("initial_state (the pool) is required with ssm_state_indices")
     if pool:

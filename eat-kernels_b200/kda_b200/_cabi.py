@@ -13,7 +13,8 @@ STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
 NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
 KERNEL_TCGEN05, KERNEL_MMA_SYNC = 0, 1
 EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
-           "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version"]
+           "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",
+           "kda_debug_configure"]
 
 
 class KdaPrefillArgs(C.Structure):
@@ -79,6 +80,8 @@ def lib():
         L.kda_error_string.argtypes = [C.c_int]
         L.kda_error_string.restype = C.c_char_p
         L.kda_version.restype = C.c_char_p
+        L.kda_debug_configure.argtypes = [C.c_int64, C.c_int32, C.c_void_p]
+        L.kda_debug_configure.restype = C.c_int
         L.kda_abi_struct_bytes.argtypes = [C.c_int]
         L.kda_abi_struct_bytes.restype = C.c_size_t
         if (L.kda_abi_struct_bytes(0) != C.sizeof(KdaPrefillArgs) or L.kda_abi_struct_bytes(1) != C.sizeof(KdaSegmentArgs)):

@@ -32,7 +32,7 @@ enum {
   KDA_OK = 0,
   KDA_ERR_ARG = -1,        /* null / misaligned pointer, bad stride or size */
   KDA_ERR_WORKSPACE = -2,  /* workspace too small */
-  KDA_ERR_LAUNCH = -3,     /* the CUDA runtime refused a launch (see kda_last_cuda_error) */
+  KDA_ERR_LAUNCH = -3,     /* the CUDA runtime refused a launch (kda_error_string gives its message) */
   KDA_ERR_LIMIT = -4       /* a size exceeds a documented maximum */
 };
 
@@ -60,7 +60,11 @@ enum {
   KDA_STATUS_BAD_CU = 1,        /* cu_seqlens rejected: every sequence treated as empty, output rows zero-filled */
   KDA_STATUS_BAD_SLOT = 2,      /* bad or repeated ssm_state_indices entry: that sequence's state goes to scratch */
   KDA_STATUS_BAD_SOURCE = 4,    /* bad initial_state_indices entry */
-  KDA_STATUS_BAD_CKPT = 8       /* checkpoint rows outside state_checkpoints or overlapping an earlier sequence */
+  KDA_STATUS_BAD_CKPT = 8,      /* checkpoint rows outside state_checkpoints or overlapping an earlier sequence */
+  KDA_STATUS_RANGE = 16         /* not a table error and not in the reference: some key channel decayed by more than
+                                   2^126 within 16 tokens (impossible with the raw front-end's -5 bound; possible with
+                                   unbounded plain-call log-decays), the exponents of that chunk's intra-chunk products
+                                   were clamped and the results of that (sequence, head) are inexact */
 };
 
 typedef struct KdaPrefillArgs {
@@ -185,6 +189,16 @@ size_t kda_abi_struct_bytes(int which);
 
 /* Library version and build information ("kda_b200 <n> sm_100a"). */
 const char* kda_version(void);
+
+/* Diagnostics for tests and profiling runs; process-wide, not thread-safe, never needed by a product call.  No
+ * counterpart in the reference (whose waits trap after 60 s, kda/b200/README.md:169-171).
+ *   wait_limit_us  bound of every wait inside the tcgen05 kernel (0 = the built-in two seconds).  When a wait runs out
+ *                  the kernel finishes its control flow, waits for its own copies and tensor-core work, frees tensor
+ *                  memory and writes a code to status[2].
+ *   flags          bit 0: the kernel's loader never issues the v copies, so that a waiter runs into the bound
+ *                  (used to test the give-up path without faulting or hanging anything); 0 = normal operation.
+ *   prof_counters  device uint64[1024] receiving per-role cycle counters in builds compiled with -DKDA_PROF; NULL else. */
+int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters);
 
 #ifdef __cplusplus
 }

@@ -58,3 +58,39 @@ def to_dev(inputs, device=DEV):
 def partition(rng: random.Random, T, N):
     cuts = sorted(rng.sample(range(1, T), N - 1))
     return [b - a for a, b in zip([0, *cuts], [*cuts, T])]
+
+
+def plain_on_device(H, T, seed, g_mean=0.0, device=DEV):
+    """Pre-activated inputs of the benchmark configurations, drawn on the device: q, k ~ N(0,1) L2-normalised per head
+    then bf16, v ~ N(0,1) bf16, g = logsigmoid(N(g_mean, 1)) fp32, beta = sigmoid(N(0,1)) fp32."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    q = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=device), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(1, T, H, D, generator=gen, device=device), dim=-1).to(torch.bfloat16)
+    v = torch.randn(1, T, H, D, generator=gen, device=device).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, D, generator=gen, device=device) + g_mean)
+    beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device=device))
+    return q, k, v, g, beta
+
+
+def gold_plain(q, k, v, g, beta, scale, init, lens, every=0):
+    """fp64 recurrence of the pre-activated call on the CPU (C oracle; state key-first), with checkpoint rows chained
+    over segments when every > 0: returns (out, final states, rows or None)."""
+    if not every:
+        o, f = c_oracle.recurrence_plain(q, k, v, g, beta, scale, init, [0, *np.cumsum(lens).tolist()])
+        return o, f, None
+    # one oracle call per checkpoint interval "wave": segment j of every sequence that still has one
+    outs = torch.zeros(q.shape, dtype=torch.float32)
+    S = init.clone()
+    rows = [[] for _ in lens]
+    starts = [0, *np.cumsum(lens).tolist()]
+    for j in range(-(-max(lens) // every)):
+        segs = [(n, starts[n] + j * every, starts[n] + min(lens[n], (j + 1) * every)) for n in range(len(lens)) if j * every < lens[n]]
+        for n, _, _ in segs:
+            rows[n].append(S[n].clone())
+        tok = torch.cat([torch.arange(a, b) for _, a, b in segs])
+        cu = [0, *np.cumsum([b - a for _, a, b in segs]).tolist()]
+        ids = [n for n, _, _ in segs]
+        o, f = c_oracle.recurrence_plain(q[:, tok], k[:, tok], v[:, tok], g[:, tok], beta[:, tok], scale, S[ids], cu)
+        outs[:, tok] = o
+        S[ids] = f
+    return outs, S, torch.stack([r for rs in rows for r in rs])
