@@ -39,9 +39,10 @@ CK_EVERY = 1024
 FLOP_PER_TOKEN_HEAD = 6 * D * D + 4 * 64 * (D + D)          # 163 840, canonical chunk 64
 BYTES_PER_TOKEN_HEAD = 3 * D * 2 + D * 4 + 4 + D * 2         # q,k,v bf16 + g fp32 + beta fp32 + out bf16 = 1540
 METRIC = "KDA prefill tokens/s (H=64,K=V=128 varlen)"
-# dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_umma_kernel per token-head, from the ncu capture of
-# `bench.py --small` summarised under profiles/ (traffic grows in proportion to token-heads); None until captured.
-NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1701.6   # profiles/kda_chunk_umma_serving.md, section 2
+# dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_umma_kernel per token-head, taken from one ncu capture of
+# `bench.py --small` (DRAM traffic grows in proportion to token-heads: the kernel streams every operand once).  A
+# constant from that capture, not a live measurement: counters cannot be read inside a timed run.
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1701.6
 
 
 def workload_lengths(seed=2):
@@ -54,8 +55,9 @@ def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         j = json.loads(p.read_text())
-        return {"hbm_gbs": float(j["hbm_gbs"]), "tf": float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "src": "measured"}
-    return {"hbm_gbs": 6650.0, "tf": 1400.0, "src": "fallback"}
+        return {"hbm_gbs": float(j["hbm_gbs"]), "tf": float(j.get("bf16_tflops_sustained", j["bf16_tflops"])),
+                "tf_burst": float(j["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tf": 1400.0, "tf_burst": 1590.0, "src": "fallback"}
 
 
 class ClockSampler:
@@ -109,13 +111,61 @@ def make_device_inputs(H, lens, seed, dev):
     return q, k, v, g, beta
 
 
+def _oracle():
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import c_oracle
+    import kda_oracle as ko
+    return c_oracle, ko
+
+
+def verify_serving(tensors, lens, pool0, slots, ck_every, result, heads):
+    """Checks one prefill of the serving workload against the fp64 recurrence on a subset of heads (heads are independent,
+    so a head slice of the inputs is a complete problem for the CPU oracle): output rows, the touched pool slots and the
+    checkpoint rows.  Same acceptance test as the parity suite (every element within half the gold RMS or 5 % of its
+    magnitude, relative L2 < 1e-2).  Returns the largest relative L2 seen; raises SystemExit on a mismatch."""
+    c_oracle, ko = _oracle()
+    q, k, v, g, beta = (t[:, :, heads].cpu() for t in tensors)
+    out, pool, ck = result
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    S = pool0[slots.long()][:, heads].cpu()
+    gold_o = torch.zeros(q.shape, dtype=torch.float32)
+    rows = [[] for _ in lens]
+    waves = -(-max(lens) // ck_every) if ck_every else 1
+    for j in range(waves):          # segment j of every sequence that still has one: one oracle call per wave
+        step = ck_every if ck_every else max(lens)
+        segs = [(n, starts[n] + j * step, starts[n] + min(lens[n], (j + 1) * step)) for n in range(len(lens)) if j * step < lens[n]]
+        ids = [n for n, _, _ in segs]
+        for n in ids:
+            rows[n].append(S[n].clone())
+        tok = torch.cat([torch.arange(a, b) for _, a, b in segs])
+        cu = [0]
+        for _, a, b in segs:
+            cu.append(cu[-1] + b - a)
+        o, f = c_oracle.recurrence_plain(q[:, tok], k[:, tok], v[:, tok], g[:, tok], beta[:, tok], D ** -0.5, S[ids], cu)
+        gold_o[:, tok] = o
+        S[ids] = f
+    worst = 0.0
+    try:
+        worst = max(worst, ko.check_close(out[:, :, heads].float().cpu(), gold_o, "bench verification: output")[1])
+        worst = max(worst, ko.check_close(pool[slots.long()][:, heads].cpu(), S, "bench verification: pool slots")[1])
+        if ck_every:
+            gold_ck = torch.stack([r for rs in rows for r in rs])
+            worst = max(worst, ko.check_close(ck[:, heads].float().cpu(), gold_ck, "bench verification: checkpoint rows")[1])
+    except AssertionError as e:
+        raise SystemExit(f"bench: {e}")
+    return worst
+
+
 def cpu_baseline(lens, H, target_s=12.0):
     """The oracle's C restatement of the reference recurrence (fp32 working precision, OpenMP over sequence-heads) on
     a bounded prefix of the same workload; returns the cpu_baseline object."""
     sys.path.insert(0, str(ROOT / "oracle"))
     import c_oracle
     import kda_oracle as ko
-    threads = c_oracle.threads("f32")
+    # every host CPU, whatever OMP_NUM_THREADS says (torch.distributed.run exports OMP_NUM_THREADS=1 to its children)
+    threads = c_oracle.set_threads(0, "f32")
 
     def run(n_tok):
         sample_lens, left = [], n_tok
@@ -166,7 +216,8 @@ def run_reference(args, lens):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "configs[2] serving call H=64 K=V=128, 48 requests lognormal lengths; CPU arm runs "
-                                   f"a prefix of {n} tokens per step", "heads": H_TOTAL},
+                                   f"a prefix of {n} tokens per step (tokens/s is per token, so the sample is comparable)",
+                       "heads": H_TOTAL, "same_config": "prefix sample of the same workload", "threads": base["cores"]},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -309,9 +360,11 @@ def run_headline(args, dev, kda_b200):
     return 0
 
 
-def run_longctx(args, world, rank, dev, kda_b200):
+def measure_longctx(args, world, rank, dev, steps, warmup, verify=True):
     """configs[3]: one sequence of 131072 tokens, H = 96, slow decay g = logsigmoid(N(2,1)), zero initial state; the
-    tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up."""
+    tokens are sharded over the ranks, per-rank affine state maps are all-gathered over NCCL, scanned and fixed up.
+    Returns the measurement as a dict on rank 0 (None elsewhere).  With `verify` two heads of the whole sequence are
+    checked against the fp64 recurrence on rank 0's host (every rank ships those heads' inputs and output rows)."""
     import torch.distributed as dist
     from kda_b200 import parallel
     T_total, H = args.longctx_tokens, 96
@@ -334,23 +387,47 @@ def run_longctx(args, world, rank, dev, kda_b200):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(max(1, warmup)):
         out, fin = step()
     barrier()
+    verification = None
+    if verify:
+        heads = [0, H - 1]
+        mine = [t[:, :, heads].cpu() for t in (q, k, v, g, beta, out)]
+        if world > 1:
+            gathered = [None] * world if rank == 0 else None
+            dist.gather_object(mine, gathered, dst=0)
+        else:
+            gathered = [mine]
+        if rank == 0:
+            c_oracle, ko = _oracle()
+            c_oracle.set_threads(0)
+            full = [torch.cat([r[i] for r in gathered], dim=1) for i in range(6)]
+            gold_o, gold_s = c_oracle.recurrence_plain(*full[:5], D ** -0.5, None, None)
+            try:
+                r1 = ko.check_close(full[5].float(), gold_o, "bench verification (configs[3]): output of every rank")[1]
+                r2 = ko.check_close(fin[:, heads].transpose(-1, -2).cpu(), gold_s, "bench verification (configs[3]): final state")[1]
+            except AssertionError as e:
+                raise SystemExit(f"bench: {e}")
+            verification = {"verified": True, "rel_l2_max": max(r1, r2), "heads_checked": heads,
+                            "what": "output rows of every rank and the final state vs the fp64 recurrence"}
+        barrier()
     sampler = ClockSampler(dev.index) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         out, fin = step()
     e1.record()
     barrier()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     finite = bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(fin).all())
+    if not finite:
+        raise SystemExit("bench: the context-parallel call produced non-finite values")
     clocks = sampler.stop() if sampler else None
     # one more step with CUDA events at the phase boundaries (this rank's view; not part of the timed region)
     ev = []
@@ -360,24 +437,33 @@ def run_longctx(args, world, rank, dev, kda_b200):
     bounds = parallel.plan_bounds(T, H, rank == 0) if pieces <= 0 else parallel.split_pieces(T, pieces)
     mapped_tokens = T - (bounds[1] if rank == 0 else 0)
     fix_bytes = mapped_tokens * H * 3 * D * 2 + (len(bounds) - 1 - (1 if rank == 0 else 0)) * H * D * D * 4
+    if rank != 0:
+        return None
+    pk = peaks()
+    flops = T_total * H * FLOP_PER_TOKEN_HEAD
+    algo_bytes = T_total * H * BYTES_PER_TOKEN_HEAD + H * 2 * D * D * 4
+    return {
+        "metric": f"KDA prefill tokens/s (H=96,K=V=128, one {T_total}-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"configs[3]: T={T_total}, H=96, g=logsigmoid(N(2,1)), zero initial state", "piece_bounds_rank0": bounds,
+                   "tokens_per_rank": shards, "parallelism": f"cp{world}", "finite": finite},
+        "verification": verification, "verified": bool(verification),
+        "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
+        "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
+                   "frac": flops / (ms * 1e-3) / 1e12 / pk["tf"]},
+        "phases_ms_rank0": phases,
+        "fixup": {"bytes": fix_bytes, "GB/s": (fix_bytes / (phases["fixup"] * 1e-3) / 1e9) if phases.get("fixup", 0) > 0 else None,
+                  "note": "o_loc + Qt read, out written (768 B per mapped token-head) plus the entering states"},
+        "clocks": clocks}
+
+
+def run_longctx(args, world, rank, dev, kda_b200):
+    import torch.distributed as dist
+    line = measure_longctx(args, world, rank, dev, args.steps, args.warmup, verify=not args.no_verify)
     if rank == 0:
-        pk = peaks()
-        flops = T_total * H * FLOP_PER_TOKEN_HEAD
-        algo_bytes = T_total * H * BYTES_PER_TOKEN_HEAD + H * 2 * D * D * 4
-        print(json.dumps({
-            "metric": f"KDA prefill tokens/s (H=96,K=V=128, one {T_total}-token sequence, context-parallel)", "value": T_total / (ms * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"configs[3]: T={T_total}, H=96, g=logsigmoid(N(2,1)), zero initial state", "piece_bounds_rank0": bounds,
-                       "tokens_per_rank": shards, "parallelism": f"cp{world}", "finite": finite},
-            "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
-            "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
-                       "frac": flops / (ms * 1e-3) / 1e12 / pk["tf"]},
-            "phases_ms_rank0": phases,
-            "fixup": {"bytes": fix_bytes, "GB/s": (fix_bytes / (phases["fixup"] * 1e-3) / 1e9) if phases.get("fixup", 0) > 0 else None,
-                      "note": "o_loc + Qt read, out written (768 B per mapped token-head) plus the entering states"},
-            "clocks": clocks}))
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -392,6 +478,8 @@ def main(argv=None):
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-groups", type=int, default=6, help="end-to-end arm: request groups whose copies and prefills overlap")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle verification before timing (profiler captures)")
+    ap.add_argument("--no-longctx", action="store_true", help="N > 1: skip the context-parallel configs[3] measurement")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
     ap.add_argument("--workload", default="serving", choices=["serving", "longctx", "layouts", "headline"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
@@ -449,6 +537,30 @@ def main(argv=None):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- verification, before timing and again after an in-place refill of every input (the launch re-reads the same
+    # buffers), as the reference's own benchmark does (kda/b200/bench.py:182-187): two heads of this rank's shard
+    # against the fp64 recurrence on the CPU.
+    verified = None
+    if not args.no_verify:
+        heads = sorted({0, H - 1})
+        pool0 = pool.clone()
+        res = launch()
+        torch.cuda.synchronize()
+        rel = verify_serving((q, k, v, g, beta), lens, pool0, slots, CK_EVERY, res, heads)
+        q2, k2, v2, g2, beta2 = make_device_inputs(H, lens, 500 + rank, dev)
+        for dst_, src_ in ((q, q2), (k, k2), (v, v2), (g, g2), (beta, beta2)):
+            dst_.copy_(src_)
+        del q2, k2, v2, g2, beta2
+        pool.copy_(pool0)
+        ck.zero_()
+        res = launch()
+        torch.cuda.synchronize()
+        rel = max(rel, verify_serving((q, k, v, g, beta), lens, pool0, slots, CK_EVERY, res, heads))
+        del pool0
+        verified = {"verified": True, "rel_l2_max": rel, "heads_checked": heads,
+                    "what": "output, touched pool slots and bf16 checkpoint rows vs the fp64 recurrence, before timing "
+                            "and after an in-place refill of q, k, v, g, beta"}
 
     sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
@@ -542,6 +654,19 @@ def main(argv=None):
         e2e = {"value": T / (ems * 1e-3), "unit": "tokens/s", "ms_per_step": ems, "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": d2h * world, "groups": len(groups)}
 
+    # ---- N > 1: the context-parallel configuration (configs[3]) as well, after the headline timing, so that one
+    # launch per N yields both scaling curves.  The serving tensors are released first.
+    longctx = None
+    if world > 1 and not args.no_longctx and not args.small:
+        del launch, q, k, v, g, beta, pool, ck
+        if args.e2e_steps > 0:
+            del groups, out_host
+        torch.cuda.empty_cache()
+        lc = measure_longctx(args, world, rank, dev, max(3, min(args.steps, 5)), 2, verify=not args.no_verify)
+        if rank == 0:
+            longctx = {kk: lc[kk] for kk in ("metric", "value", "unit", "ms_per_step", "steps", "config", "verification",
+                                               "verified", "roofline", "phases_ms_rank0", "fixup")}
+
     if rank == 0:
         pk = peaks()
         algo_bytes = T * H * BYTES_PER_TOKEN_HEAD + N * H * 2 * D * D * 4 + rows * H * D * D * 2
@@ -562,9 +687,16 @@ def main(argv=None):
                          "kernel": "kda_chunk_umma_kernel (the step also holds kda_plan_kernel, 0.9 % of the time)",
                          "algorithmic_bytes_per_launch": algo_bytes},
             "tensor": {"achieved": tf, "peak": pk["tf"], "unit": "TFLOP/s", "frac": tf / pk["tf"],
-                       "flops_per_launch": flops, "note": "dense count 163840 FLOP per token-head (chunk 64 convention)"},
+                       "peak_burst": pk["tf_burst"], "frac_of_burst": tf / pk["tf_burst"],
+                       "flops_per_launch": flops,
+                       "note": "dense count 163840 FLOP per token-head (chunk 64 convention); `peak` is the sustained "
+                               "bf16 figure, `peak_burst` the burst one: the timed region lies between the two definitions"},
             "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks,
         }
+        if verified is not None:
+            line.update(verified=True, verification=verified)
+        if longctx is not None:
+            line["longctx"] = longctx
         if NCU_DRAM_BYTES_PER_TOKEN_HEAD is not None:
             line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_TOKEN_HEAD * T * H
         if world == 1 and not args.no_cpu_baseline:

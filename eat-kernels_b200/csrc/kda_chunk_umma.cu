@@ -536,12 +536,14 @@ __device__ void role_inverse(const ChunkParams& p, const Ctx& x, uint32_t tmem, 
       uint32_t r[16];
       tmem_ld16(tq + 32 * s + 16 * hb, r);
       tmem_wait_ld();
-      const float bs = (hb == 1 && lane < 16) ? 0.0f : beta;
+      const bool zero = hb == 1 && lane < 16;      // a select, not a product with 0: the products above the diagonal
+                                                   // pair a grown factor with a grown one and may be infinite
 #pragma unroll
       for (int j4 = 0; j4 < 4; j4++) {
         const int j = 16 * hb + 4 * j4;
-        const float4 f = make_float4(__uint_as_float(r[4 * j4 + 0]) * bs, __uint_as_float(r[4 * j4 + 1]) * bs,
-                                     __uint_as_float(r[4 * j4 + 2]) * bs, __uint_as_float(r[4 * j4 + 3]) * bs);
+        float4 f = make_float4(__uint_as_float(r[4 * j4 + 0]) * beta, __uint_as_float(r[4 * j4 + 1]) * beta,
+                               __uint_as_float(r[4 * j4 + 2]) * beta, __uint_as_float(r[4 * j4 + 3]) * beta);
+        if (zero) f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         *reinterpret_cast<float4*>(Lsm + lane * C + (((j >> 2) ^ (lane & 7)) << 2)) = f;
       }
     }

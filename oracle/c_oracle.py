@@ -43,6 +43,11 @@ def threads(precision="f64"):
     return lib(precision).kda_oracle_threads()
 
 
+def set_threads(n=0, precision="f64"):
+    """OpenMP threads of later calls of this precision's library (0 = every host CPU, whatever OMP_NUM_THREADS says)."""
+    return lib(precision).kda_oracle_set_threads(int(n))
+
+
 def recurrence_raw(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens, lower_bound=-5.0,
                    precision="f64"):
     """Same contract as kda_oracle.kda_recurrence: returns (out bf16 [1,T,H,128], final fp32 value-first)."""

@@ -36,6 +36,19 @@ int kda_oracle_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP thread count of later calls (n <= 0: every host CPU).  Launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1 to their children; a caller that wants all host cores for the CPU baseline has to say so. */
+int kda_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n <= 0) n = omp_get_num_procs();
+  omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* One (sequence, head): tokens t0..t1-1 of a packed [T][H][128] layout.  S is key-first [128][128], updated in place.
  * qn, kn: normalised; a: log-decay; b: beta in (0,1).  out may be NULL. */
 static void recur_one(const REAL* qn, const REAL* kn, const float* v, const REAL* a, const REAL* b, REAL scale,
