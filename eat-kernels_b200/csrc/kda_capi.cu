@@ -27,24 +27,51 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 struct Workspace {
   kda::Task* tasks;
   kda::Task* tasks_unsorted;
-  int* n_tasks;
+  int* n_tasks;            // [0] first launch, [1] second launch, [2] scan chains
   long long* cu_safe;
   float* trash;
+  // only with cuts (max_pieces > 0)
+  kda::Task* tasks_b;
+  kda::ScanChain* chains;
+  float *map_P, *map_L, *map_E;
   size_t bytes;
 };
 
-Workspace carve(void* base, int N, int H) {
+// `pieces`: capacity for the pieces of cut sequences (0 = the call never cuts; the layout is then the one older
+// callers sized their workspace for)
+Workspace carve(void* base, int N, int H, int pieces = 0) {
   Workspace w;
   size_t off = 0;
   uint8_t* b = reinterpret_cast<uint8_t*>(base);
   const size_t n = (size_t)(N > 0 ? N : 1);
-  w.tasks = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + n * sizeof(kda::Task), 256);
+  const size_t na = n + 2 * (size_t)pieces;
+  w.tasks = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + na * sizeof(kda::Task), 256);
   w.tasks_unsorted = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + n * sizeof(kda::Task), 256);
   w.n_tasks = reinterpret_cast<int*>(b + off); off = align_up(off + 16, 256);
   w.cu_safe = reinterpret_cast<long long*>(b + off); off = align_up(off + (n + 1) * sizeof(long long), 256);
   w.trash = reinterpret_cast<float*>(b + off); off = align_up(off + (size_t)H * kda::STATE_ELEMS * sizeof(float), 256);
+  w.tasks_b = nullptr; w.chains = nullptr; w.map_P = w.map_L = w.map_E = nullptr;
+  if (pieces > 0) {
+    const size_t maps = (size_t)pieces * H * kda::STATE_ELEMS * sizeof(float);
+    w.tasks_b = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + (n + pieces) * sizeof(kda::Task), 256);
+    w.chains = reinterpret_cast<kda::ScanChain*>(b + off); off = align_up(off + ((size_t)pieces / 2 + 1) * sizeof(kda::ScanChain), 256);
+    w.map_P = reinterpret_cast<float*>(b + off); off = align_up(off + maps, 256);
+    w.map_L = reinterpret_cast<float*>(b + off); off = align_up(off + maps, 256);
+    w.map_E = reinterpret_cast<float*>(b + off); off = align_up(off + maps, 256);
+  }
   w.bytes = off;
   return w;
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+  }
+  return cached[dev];
 }
 
 int check_tokens(const KdaPrefillArgs* a) {
@@ -143,6 +170,11 @@ size_t kda_prefill_workspace_bytes(int32_t N, int32_t H) {
   return carve(nullptr, N, H).bytes;
 }
 
+size_t kda_prefill_workspace_bytes_cuts(int32_t N, int32_t H, int32_t max_cut_pieces) {
+  if (N < 0 || H <= 0 || max_cut_pieces < 0 || max_cut_pieces > KDA_MAX_CUT_PIECES) return 0;
+  return carve(nullptr, N, H, max_cut_pieces).bytes;
+}
+
 int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   int rc = check_tokens(a);
@@ -156,7 +188,9 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   }
   if (a->src_base && (!aligned16(a->src_base) || (a->src_slot_stride & 3))) return KDA_ERR_ARG;
   if (a->dst_base && (!aligned16(a->dst_base) || (a->dst_slot_stride & 3))) return KDA_ERR_ARG;
-  const Workspace w = carve(a->workspace, a->N, a->H);
+  if (a->max_cut_pieces < 0 || a->max_cut_pieces > KDA_MAX_CUT_PIECES) return KDA_ERR_ARG;
+  const int pieces = a->max_cut_pieces >= 2 ? a->max_cut_pieces : 0;
+  const Workspace w = carve(a->workspace, a->N, a->H, pieces);
   if (a->workspace_bytes < w.bytes) return KDA_ERR_WORKSPACE;
 
   kda::PlanParams pl;
@@ -173,6 +207,11 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   pl.ck_starts = a->ck_starts; pl.ck_is64 = a->ck_starts_is64;
   pl.trash = w.trash; pl.cu_safe = w.cu_safe; pl.tasks_unsorted = w.tasks_unsorted; pl.tasks = w.tasks;
   pl.n_tasks = w.n_tasks; pl.status = a->status;
+  pl.max_pieces = pieces; pl.n_sm = sm_count(); pl.key_first = a->state_layout == KDA_STATE_KEY_FIRST;
+  if (pieces > 0) {
+    pl.tasks_b = w.tasks_b; pl.n_tasks_b = w.n_tasks + 1; pl.n_chains = w.n_tasks + 2; pl.chains = w.chains;
+    pl.map_P = w.map_P; pl.map_L = w.map_L; pl.map_E = w.map_E;
+  }
   cudaError_t e = kda::launch_plan(pl, stream);
   if (e != cudaSuccess) return cuda_fail(e);
 
@@ -183,15 +222,24 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   p.ck_row_stride = (long long)a->H * kda::STATE_ELEMS;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
-  if (a->kernel == KDA_KERNEL_MMA_SYNC) {
-    e = kda::launch_chunk_fwd(p, a->N, stream);
-  } else {
-    kda::TmaMaps maps;
+  kda::TmaMaps maps;
+  const bool umma = a->kernel != KDA_KERNEL_MMA_SYNC;
+  if (umma) {
     rc = fill_tma_maps(maps, a);
     if (rc != KDA_OK) return rc;
-    e = kda::launch_chunk_umma(p, maps, a->N, stream);
   }
+  // first launch: every uncut sequence (or all of them), piece 0 and the map chains of the cut ones
+  e = umma ? kda::launch_chunk_umma(p, maps, a->N + 2 * pieces, stream) : kda::launch_chunk_fwd(p, a->N + 2 * pieces, stream);
   if (e != cudaSuccess) return cuda_fail(e);
+  if (pieces > 0) {
+    // entering states of the later pieces, then those pieces (both launches find nothing to do when nothing was cut)
+    e = kda::launch_scan_chains(w.chains, w.n_tasks + 2, pieces / 2 + 1, w.map_P, w.map_L, w.map_E, a->H, p.key_first, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    p.tasks = w.tasks_b;
+    p.n_tasks = w.n_tasks + 1;
+    e = umma ? kda::launch_chunk_umma(p, maps, a->N + pieces, stream) : kda::launch_chunk_fwd(p, a->N + pieces, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   return KDA_OK;
 }
 
@@ -230,6 +278,7 @@ int kda_prefill_launch_noalloc(const KdaPrefillArgs* a, void* stream_) {
   KdaPrefillArgs b = *a;
   b.workspace = g_noalloc_addr[dev];
   b.workspace_bytes = kNoallocBytes;
+  b.max_cut_pieces = 0;                       // the fixed array has no room for state maps: this entry point never cuts
   return kda_prefill_launch(&b, stream_);
 }
 
@@ -318,7 +367,19 @@ const char* kda_error_string(int code) {
 
 size_t kda_abi_struct_bytes(int which) { return which == 0 ? sizeof(KdaPrefillArgs) : (which == 1 ? sizeof(KdaSegmentArgs) : 0); }
 
-const char* kda_version(void) { return "kda_b200 2 sm_100a"; }
+const char* kda_version(void) { return "kda_b200 3 sm_100a"; }
+
+int kda_prefill_plan_counts(const KdaPrefillArgs* a, int32_t* counts, void* stream_) {
+  if (a == nullptr || counts == nullptr || a->workspace == nullptr || a->H <= 0 || a->N < 1) return KDA_ERR_ARG;
+  if (a->max_cut_pieces < 0 || a->max_cut_pieces > KDA_MAX_CUT_PIECES) return KDA_ERR_ARG;
+  const int pieces = a->max_cut_pieces >= 2 ? a->max_cut_pieces : 0;
+  const Workspace w = carve(a->workspace, a->N, a->H, pieces);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  counts[0] = counts[1] = counts[2] = 0;
+  cudaError_t e = cudaMemcpyAsync(counts, w.n_tasks, (pieces > 0 ? 3 : 1) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
 
 int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters) {
   if (wait_limit_us < 0 || (flags & ~kda::DBG_SKIP_V_STREAM)) return KDA_ERR_ARG;

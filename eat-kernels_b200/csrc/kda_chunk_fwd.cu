@@ -553,7 +553,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_fwd_kernel(const ChunkPa
   }
 
   if (warp < STATE_WARPS && task.dst != nullptr)
-    store_state_t<float>(S, task.dst + (size_t)h * STATE_ELEMS, p.key_first, warp, lane);
+    store_state_t<float>(S, task.dst + (size_t)h * STATE_ELEMS, p.key_first && !(task.flags & TF_DST_VF), warp, lane);
 }
 
 cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream) {

@@ -823,7 +823,8 @@ __device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, 
       void* ckp = nullptr;
       if (ck) ckp = p.ck_is_bf16 ? static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(task.ck) + ck_off)
                                  : static_cast<void*>(reinterpret_cast<float*>(task.ck) + ck_off);
-      store_state_rows<KF>(tS, dst, ckp, p.ck_is_bf16, v, hf);
+      if (KF && (task.flags & TF_DST_VF)) store_state_rows<0>(tS, dst, ckp, p.ck_is_bf16, v, hf);   // transition maps
+      else store_state_rows<KF>(tS, dst, ckp, p.ck_is_bf16, v, hf);
     }
     if (last) break;
     {

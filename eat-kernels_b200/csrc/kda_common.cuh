@@ -18,6 +18,8 @@ constexpr uint32_t TF_INIT_IDENTITY = 2u;  // start from S = I (transition chain
 constexpr uint32_t TF_V_ZERO = 4u;         // treat v as 0 (transition chain)
 constexpr uint32_t TF_OUT_AUX = 8u;        // write output rows to the auxiliary tensor (Qt)
 constexpr uint32_t TF_NO_OUT = 16u;        // do not write output rows
+constexpr uint32_t TF_DST_VF = 32u;        // store the final state value-first whatever the launch's state layout
+                                           // (transition maps: the scan applies them as  E <- E P)
 
 // One unit of work of the fused chunk kernel: a run of tokens of one sequence (all heads).
 struct __align__(16) Task {

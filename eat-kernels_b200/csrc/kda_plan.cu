@@ -19,6 +19,14 @@ namespace kda {
 
 constexpr int PLAN_THREADS = 1024;
 constexpr int SORT_MAX = 4096;
+// cut planning
+constexpr int CUT_MAX_SEQS = 1024;       // sequences a cut plan is made for (beyond: never cut)
+constexpr int N_CAND = 9;                // candidate piece lengths
+constexpr int MIN_PIECE_CHUNKS = 16;     // shorter pieces drown in the per-task cost
+constexpr int TASK_OVERHEAD = 3;         // start / end of a task, in chunk steps
+constexpr int SCAN_STEPS_X16 = 12;       // one map of the scan chain, in 1/16 chunk steps
+constexpr int LAUNCH_STEPS = 4;          // the scan launch and the second kernel launch, in chunk steps
+__host__ __device__ constexpr int cand_pieces(int k) { return k < 3 ? k + 2 : (k == 3 ? 6 : (k == 4 ? 8 : (k == 5 ? 12 : (k == 6 ? 16 : (k == 7 ? 24 : 32))))); }
 
 __device__ __forceinline__ long long rd_table(const void* p, int is64, long long i) {
   return is64 ? reinterpret_cast<const long long*>(p)[i] : (long long)reinterpret_cast<const int*>(p)[i];
@@ -28,6 +36,9 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
   __shared__ unsigned long long keys[SORT_MAX];
   __shared__ unsigned char s_keep[SORT_MAX];     // checkpoint rows of sequence i: 0 = none / rejected, 1 = kept
   __shared__ int s_bits, s_overlap;
+  __shared__ int s_lp, s_cmax, s_uncut_work, s_work[N_CAND], s_pieces[N_CAND], s_longest[N_CAND];
+  __shared__ unsigned short s_off_a[CUT_MAX_SEQS], s_off_b[CUT_MAX_SEQS];
+  __shared__ unsigned char s_cnt_a[CUT_MAX_SEQS], s_cnt_b[CUT_MAX_SEQS], s_off_m[CUT_MAX_SEQS], s_off_c[CUT_MAX_SEQS];
   const int tid = threadIdx.x, bd = blockDim.x, N = a.N;
   if (tid == 0) { s_bits = 0; s_overlap = 0; }
   __syncthreads();
@@ -172,12 +183,197 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
     }
   }
   __syncthreads();   // tasks_unsorted complete
-  for (int i = tid; i < N; i += bd) {
-    const int srcpos = sorted ? (int)(keys[i] & 0xffffffffu) : i;
-    a.tasks[i] = a.tasks_unsorted[srcpos];
+
+  // ---- cuts.  A long sequence is a serial chain of chunks on one SM per head; when such chains, not the total work,
+  // bound the launch (few heads per GPU, one long request among short ones), cutting them into pieces of `lp` chunks
+  // shortens the launch although a cut sequence costs about three times its chunks (see PlanParams).  The piece length
+  // is chosen among "the longest sequence in 2, 3, 4, 6, ... pieces" by a cost model in chunk steps, against not
+  // cutting at all.  Pieces are multiples of the checkpoint interval, so every checkpoint row is written by the piece
+  // that holds its token.  Function of the reference's host planners (kda/b200/csrc/w3/base/kernel.py:389-444,482-532)
+  // and of its device planner (kda/b200/csrc/dyn/plan_cp.cu:476-488).
+  const int au = (a.ck_base != nullptr && a.ck_every > 0) ? a.ck_every / C : 1;    // alignment of a cut, in chunks
+  if (tid == 0) s_lp = 0;
+  if (a.max_pieces >= 2 && sorted && N <= CUT_MAX_SEQS && !noop) {
+    if (tid < N_CAND) { s_work[tid] = 0; s_pieces[tid] = 0; s_longest[tid] = 0; }
+    if (tid == 0) { s_uncut_work = 0; s_cmax = (int)((0x7fffffffULL - (keys[0] >> 32)) + C - 1) / C; }
+    __syncthreads();
+    const int cmax = s_cmax;
+    int lp_of[N_CAND];
+#pragma unroll
+    for (int k = 0; k < N_CAND; k++) {
+      const int p = cand_pieces(k);
+      int lp = (cmax + p - 1) / p;
+      lp = (lp + au - 1) / au * au;
+      lp_of[k] = (lp >= MIN_PIECE_CHUNKS && lp < cmax) ? lp : 0;
+    }
+    for (int j = tid; j < N; j += bd) {
+      const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
+      atomicAdd(&s_uncut_work, c > 0 ? c + TASK_OVERHEAD : 0);
+#pragma unroll
+      for (int k = 0; k < N_CAND; k++) {
+        const int lp = lp_of[k];
+        if (lp == 0) continue;
+        if (c <= lp + lp / 4) {
+          if (c > 0) atomicAdd(&s_work[k], c + TASK_OVERHEAD);
+          atomicMax(&s_longest[k], c);
+        } else {
+          const int p = (c + lp - 1) / lp;
+          atomicAdd(&s_work[k], (lp + TASK_OVERHEAD) * (3 * p - 4));      // 1 + 2 (p - 2) tasks, then p - 1 tasks
+          atomicAdd(&s_pieces[k], p);
+          atomicMax(&s_longest[k], lp);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      // times in 1/16 chunk steps; a launch cannot end before its longest task, nor before its share of the work
+      const long long H16 = 16LL * a.H;
+      long long best = max((long long)s_uncut_work * H16 / a.n_sm, 16LL * (cmax + TASK_OVERHEAD));
+      int best_lp = 0;
+      for (int k = 0; k < N_CAND; k++) {
+        const int lp = lp_of[k];
+        if (lp == 0 || s_pieces[k] == 0 || s_pieces[k] > a.max_pieces) continue;
+        const long long floor2 = 16LL * (max(s_longest[k], lp) + TASK_OVERHEAD + lp + TASK_OVERHEAD);
+        const long long t = max((long long)s_work[k] * H16 / a.n_sm, floor2) + 16LL * (SCAN_STEPS_X16 * (cand_pieces(k) - 2)) / 16 +
+                            16LL * LAUNCH_STEPS;
+        if (t * 10 < best * 9) { best = t; best_lp = lp; }          // cut only for a clear gain
+      }
+      s_lp = best_lp;
+    }
+  }
+  __syncthreads();
+  const int lp = s_lp;
+  if (lp == 0) {
+    for (int i = tid; i < N; i += bd) {
+      const int srcpos = sorted ? (int)(keys[i] & 0xffffffffu) : i;
+      a.tasks[i] = a.tasks_unsorted[srcpos];
+    }
+    if (tid == 0) {
+      *a.n_tasks = N;
+      if (a.n_tasks_b != nullptr) { *a.n_tasks_b = 0; *a.n_chains = 0; }
+    }
+  } else {
+    // Per sorted position: tasks in the first / second launch, map slots, and whether an uncut sequence moves to the
+    // second launch (the shortest ones do, until both launches carry about the same work).
+    __shared__ int s_half;
+    if (tid == 0) {
+      // work of the cut sequences per launch at the chosen piece length
+      long long wa = 0, wb = 0, uncut = 0;
+      for (int j = 0; j < N; j++) {
+        const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
+        if (c <= lp + lp / 4) uncut += c > 0 ? c + TASK_OVERHEAD : 0;
+        else {
+          const int p = (c + lp - 1) / lp;
+          wa += (long long)(lp + TASK_OVERHEAD) * (2 * p - 3);
+          wb += (long long)(lp + TASK_OVERHEAD) * (p - 1);
+        }
+      }
+      const long long to_b = ((wa + wb + uncut) / 2) - wb;      // uncut work wanted in the second launch
+      s_half = (int)max(0LL, min(uncut, to_b));
+    }
+    __syncthreads();
+    if (tid < 32) {
+      // one warp: lane l walks positions [per l, per (l + 1)) from the END of the sorted order (shortest first)
+      const int per = (N + 31) / 32;
+      int na = 0, nb = 0, nm = 0, nc = 0, wsum = 0;
+      for (int q = 0; q < per; q++) {
+        const int j = N - 1 - (tid * per + q);
+        if (j < 0) break;
+        const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
+        if (c <= lp + lp / 4) wsum += c > 0 ? c + TASK_OVERHEAD : 0;
+      }
+      int wpre = wsum;                                  // exclusive prefix of uncut work over the lanes
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, wpre, o);
+        if (tid >= o) wpre += v;
+      }
+      wpre -= wsum;
+      for (int q = 0; q < per; q++) {
+        const int j = N - 1 - (tid * per + q);
+        if (j < 0) break;
+        const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
+        unsigned char ca = 0, cb = 0;
+        if (c <= lp + lp / 4) {
+          const bool to_b = wpre < s_half && c > 0;
+          wpre += c > 0 ? c + TASK_OVERHEAD : 0;
+          if (to_b) cb = 1; else ca = 1;
+        } else {
+          const int p = (c + lp - 1) / lp;
+          ca = (unsigned char)(2 * p - 3);
+          cb = (unsigned char)(p - 1);
+          nm += p - 1;
+          nc += 1;
+        }
+        s_cnt_a[j] = ca; s_cnt_b[j] = cb;
+        na += ca; nb += cb;
+      }
+      // exclusive offsets in FORWARD (longest first) order: lane l's block lies after the blocks of the lanes above it
+      int oa = na, ob = nb, om = nm, oc = nc;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int va = __shfl_down_sync(0xffffffffu, oa, o), vb = __shfl_down_sync(0xffffffffu, ob, o);
+        const int vm = __shfl_down_sync(0xffffffffu, om, o), vc = __shfl_down_sync(0xffffffffu, oc, o);
+        if (tid + o < 32) { oa += va; ob += vb; om += vm; oc += vc; }
+      }
+      if (tid == 0) { *a.n_tasks = oa; *a.n_tasks_b = ob; *a.n_chains = oc; }
+      oa -= na; ob -= nb; om -= nm; oc -= nc;           // what the lanes above (longer sequences) take
+      // walk this lane's block forward (its LAST position is the longest sequence of the block)
+      for (int q = per - 1; q >= 0; q--) {
+        const int j = N - 1 - (tid * per + q);
+        if (j < 0) continue;
+        s_off_a[j] = (unsigned short)oa; s_off_b[j] = (unsigned short)ob; s_off_m[j] = (unsigned char)om; s_off_c[j] = (unsigned char)oc;
+        const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
+        oa += s_cnt_a[j]; ob += s_cnt_b[j];
+        if (c > lp + lp / 4) { om += (c + lp - 1) / lp - 1; oc += 1; }
+      }
+    }
+    __syncthreads();
+    const size_t slot_elems = (size_t)a.H * STATE_ELEMS;
+    for (int j = tid; j < N; j += bd) {
+      const Task t = a.tasks_unsorted[(int)(keys[j] & 0xffffffffu)];
+      const int c = (t.len + C - 1) / C;
+      if (c <= lp + lp / 4) {
+        if (s_cnt_b[j]) a.tasks_b[s_off_b[j]] = t; else a.tasks[s_off_a[j]] = t;
+        continue;
+      }
+      const int p = (c + lp - 1) / lp;
+      const int m0 = s_off_m[j];                        // slots m0 .. m0 + p - 2: slot m0 = end state of piece 0
+      int ia = s_off_a[j], ib = s_off_b[j];
+      Task u = t;                                       // piece 0: the ordinary task, cut short, end state to slot m0
+      u.len = lp * C;
+      u.dst = a.map_L + (size_t)m0 * slot_elems;
+      a.tasks[ia++] = u;
+      for (int q = 1; q < p; q++) {
+        const long long t0 = t.t0 + (long long)q * lp * C;
+        const int len = min(lp * C, t.len - q * lp * C);
+        if (q < p - 1) {                                // chains L and Tr of a middle piece -> map slot m0 + q
+          Task l;
+          l.t0 = t0; l.len = len; l.flags = TF_INIT_ZERO | TF_NO_OUT; l.src = nullptr; l.ck = nullptr; l.pad_ = 0;
+          l.dst = a.map_L + (size_t)(m0 + q) * slot_elems;
+          a.tasks[ia++] = l;
+          l.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_NO_OUT | TF_DST_VF;
+          l.dst = a.map_P + (size_t)(m0 + q) * slot_elems;
+          a.tasks[ia++] = l;
+        }
+        Task r;                                         // the piece itself, from its entering state
+        r.t0 = t0; r.len = len; r.flags = 0; r.pad_ = 0;
+        r.src = (q == 1) ? a.map_L + (size_t)m0 * slot_elems : a.map_E + (size_t)(m0 + q - 1) * slot_elems;
+        r.dst = (q == p - 1) ? t.dst : nullptr;
+        r.ck = nullptr;
+        if (t.ck != nullptr) {
+          const long long row = (long long)q * lp / au;
+          r.ck = a.ck_is_bf16 ? (void*)(reinterpret_cast<__nv_bfloat16*>(t.ck) + row * a.ck_row_stride)
+                              : (void*)(reinterpret_cast<float*>(t.ck) + row * a.ck_row_stride);
+        }
+        a.tasks_b[ib++] = r;
+      }
+      ScanChain ch;
+      ch.s0 = a.map_L + (size_t)m0 * slot_elems;
+      ch.first = m0 + 1;
+      ch.count = p - 2;
+      a.chains[s_off_c[j]] = ch;
+    }
   }
   if (tid == 0) {
-    *a.n_tasks = N;
     a.status[0] = s_bits;
     a.status[1] = 0;
     a.status[2] = 0;
@@ -187,6 +383,64 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
 
 cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream) {
   kda_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ scan of cut chains
+// Entering states of the pieces of every cut sequence: per chain and head  E[k] = E[k-1] applied to map k  with
+// E[-1] = the end state of piece 0.  In the value-first layout a state is [v][k] and a map acts as  E <- E P + L  (rows
+// v evolve independently); in the key-first layout the same relation reads  E[k'][v] = sum_k P[k][k'] E[k][v] + L[k'][v]
+// (columns v evolve independently; P is stored value-first in both cases).  A CTA carries eight independent rows /
+// columns of one head through the chain in fp32; P is read from L2 with coalesced rows.
+constexpr int SC_ROWS = 8, SC_THREADS = 256;
+
+__global__ void __launch_bounds__(SC_THREADS) kda_scan_chains_kernel(const ScanChain* __restrict__ chains, const int* __restrict__ n_chains,
+                                                                     const float* __restrict__ P, const float* __restrict__ L,
+                                                                     float* __restrict__ E, int H, int kf) {
+  __shared__ float s_cur[SC_ROWS][D];
+  if ((int)blockIdx.z >= *n_chains) return;
+  const ScanChain ch = chains[blockIdx.z];
+  if (ch.count <= 0) return;
+  const int h = blockIdx.y, r0 = blockIdx.x * SC_ROWS;
+  const int tid = threadIdx.x, row = tid >> 5, lane = tid & 31;
+  const size_t head_off = (size_t)h * STATE_ELEMS, slot_stride = (size_t)H * STATE_ELEMS;
+  const int rs = kf ? 1 : D, ks = kf ? D : 1;       // element (independent index r, contracted / produced index k)
+  const size_t base = head_off + (size_t)(r0 + row) * rs;
+  float cur[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) cur[j] = ch.s0[base + (size_t)(lane + 32 * j) * ks];
+  for (int i = 0; i < ch.count; i++) {
+    const size_t slot = (size_t)(ch.first + i) * slot_stride;
+#pragma unroll
+    for (int j = 0; j < 4; j++) s_cur[row][lane + 32 * j] = cur[j];
+    __syncthreads();
+    const float* Pi = P + slot + head_off;
+    float acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[j] = L[slot + base + (size_t)(lane + 32 * j) * ks];
+#pragma unroll 8
+    for (int k = 0; k < D; k++) {
+      const float sv = s_cur[row][k];
+      const float* pk = Pi + (size_t)k * D + lane;
+      acc[0] = fmaf(sv, pk[0], acc[0]);
+      acc[1] = fmaf(sv, pk[32], acc[1]);
+      acc[2] = fmaf(sv, pk[64], acc[2]);
+      acc[3] = fmaf(sv, pk[96], acc[3]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      cur[j] = acc[j];
+      E[slot + base + (size_t)(lane + 32 * j) * ks] = cur[j];
+    }
+  }
+}
+
+cudaError_t launch_scan_chains(const ScanChain* chains, const int* n_chains, int max_chains, const float* P, const float* L, float* E,
+                               int H, int key_first, cudaStream_t stream) {
+  if (max_chains <= 0) return cudaSuccess;
+  dim3 grid(D / SC_ROWS, H, max_chains);
+  kda_scan_chains_kernel<<<grid, SC_THREADS, 0, stream>>>(chains, n_chains, P, L, E, H, key_first);
   return cudaGetLastError();
 }
 

@@ -7,6 +7,13 @@ namespace kda {
 
 constexpr int KDA_BIT_CU = 1, KDA_BIT_SLOT = 2, KDA_BIT_SOURCE = 4, KDA_BIT_CKPT = 8, KDA_BIT_RANGE = 16;
 
+// One cut sequence for the scan: E[k] = (k == 0 ? S0 : E[k-1]) applied to map first + k, for k < count; the map slots
+// are [H][128][128] blocks `first + k` of the map arrays.
+struct ScanChain {
+  const float* s0;          // end state of piece 0 (head 0)
+  int first, count;
+};
+
 struct PlanParams {
   int N, H;
   long long T;
@@ -19,12 +26,28 @@ struct PlanParams {
   float* trash;             // [H][128][128] scratch state window for rejected destination slots
   long long* cu_safe;       // [N+1]
   Task* tasks_unsorted;     // [N]
-  Task* tasks;              // [N] longest first
+  Task* tasks;              // first launch: [N + 2 * max_pieces], longest first
   int* n_tasks;
   int* status;              // int[4]
+  // ---- cutting long sequences (max_pieces > 0).  A sequence cut into p pieces runs as: piece 0 from its true initial
+  // state and, for pieces 1 .. p-2, the two chains of the affine state map (first launch); a scan that yields the
+  // entering states of pieces 1 .. p-1; those pieces from their entering states (second launch).
+  int max_pieces;           // capacity: pieces of all cut sequences together (0 = never cut)
+  int n_sm;                 // SMs of the device (cost model)
+  int key_first;            // state layout of the launch (the transition maps are stored value-first either way)
+  Task* tasks_b;            // second launch: [N + max_pieces]
+  int* n_tasks_b;
+  float* map_P;             // [max_pieces][H][128][128] transition maps
+  float* map_L;             // [max_pieces][H][128][128] offsets; slot 0 of a cut sequence holds piece 0's end state
+  float* map_E;             // [max_pieces][H][128][128] entering states written by the scan
+  ScanChain* chains;        // [max_pieces / 3 + 1]
+  int* n_chains;
 };
 
 cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream);
+// entering states of the pieces of every cut sequence (grid sized for `max_chains`, chains beyond *n_chains exit)
+cudaError_t launch_scan_chains(const ScanChain* chains, const int* n_chains, int max_chains, const float* P, const float* L, float* E,
+                               int H, int key_first, cudaStream_t stream);
 cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);    // mma.sync kernel
 cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream);   // tcgen05 kernel
 

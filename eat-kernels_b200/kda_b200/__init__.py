@@ -166,6 +166,24 @@ class _Launch:
         _cabi.check(rc, "kda_prefill_launch")
         return self._result
 
+    def plan_counts(self):
+        """(tasks of the first launch, tasks of the second launch, cut sequences) as the device planner decided them at
+        the most recent call; the second and third are 0 when no sequence was cut.  Synchronises."""
+        counts = (C.c_int32 * 3)()
+        with torch.cuda.device(self._device):
+            stream = torch.cuda.current_stream(self._device).cuda_stream
+            _cabi.check(self._lib.kda_prefill_plan_counts(C.byref(self._args), counts, C.c_void_p(stream)), "kda_prefill_plan_counts")
+        return tuple(int(c) for c in counts)
+
+
+def cut_capacity(T, H, n_sms=148):
+    """Pieces the device planner may cut long sequences into, over the whole call (the workspace holds three 64 KB state
+    maps per piece and head).  Cutting only pays while (sequence, head) chains are too few or too uneven to fill the
+    SMs, so about two pieces per SM-and-head are plenty; calls too short to have a long chain get none."""
+    if T < 64 * CHUNK or H >= 2 * n_sms:
+        return 0
+    return int(min(_cabi.MAX_CUT_PIECES, max(2, -(-2 * n_sms // H))))
+
 
 def status_bits(launch):
     """Table-validation bits of the most recent call of a launch (0 = every caller table was valid; synchronises):
@@ -184,7 +202,8 @@ def kernel_error(launch):
 
 def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens, *, raw, key_first,
              ssm_state_indices=None, state_checkpoints=None, checkpoint_cu_starts=None, checkpoint_every_n_tokens=0,
-             initial_state_source=None, initial_state_indices=None, dynamic_layout=False, want_final=True, kernel=None):
+             initial_state_source=None, initial_state_indices=None, dynamic_layout=False, want_final=True, kernel=None,
+             max_cut_pieces=None):
     cu_seqlens = _check_args(q, k, v, g, beta, A_log, dt_bias, initial_state, cu_seqlens, dynamic_layout, raw)
     dev = q.device
     T, H = q.shape[1], q.shape[2]
@@ -283,7 +302,8 @@ def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens,
         ck_starts = _table(checkpoint_cu_starts, "checkpoint_cu_starts", N + 1, dynamic_layout)
 
     lib = _cabi.lib()
-    ws_bytes = lib.kda_prefill_workspace_bytes(N, H)
+    pieces = cut_capacity(T, H) if max_cut_pieces is None else int(max_cut_pieces)
+    ws_bytes = lib.kda_prefill_workspace_bytes_cuts(N, H, pieces)
     workspace = torch.zeros(ws_bytes + 256, dtype=torch.uint8, device=dev)
     ws_ptr = (workspace.data_ptr() + 255) // 256 * 256
     status = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -317,6 +337,7 @@ def _prepare(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, cu_seqlens,
     a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
     a.status = status.data_ptr()
     a.kernel = default_kernel() if kernel is None else int(kernel)
+    a.max_cut_pieces = pieces
 
     keep += [q_, k_, v_, g_, beta_, A_, dtb_, cu_seqlens, src, dst, d_idx, s_idx, ck, ck_starts, workspace, status, out]
     result = (out, dst) if not every else (out, dst, state_checkpoints)

@@ -12,7 +12,8 @@ FRONTEND_RAW, FRONTEND_PLAIN = 0, 1
 STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
 NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
 KERNEL_TCGEN05, KERNEL_MMA_SYNC = 0, 1
-EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_launch", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
+MAX_CUT_PIECES = 128
+EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_workspace_bytes_cuts", "kda_prefill_launch", "kda_prefill_plan_counts", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
            "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",
            "kda_debug_configure"]
 
@@ -37,6 +38,7 @@ class KdaPrefillArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
         ("kernel", C.c_int32),
+        ("max_cut_pieces", C.c_int32),
     ]
 
 
@@ -62,8 +64,12 @@ def lib():
         L = C.CDLL(str(LIB_PATH))
         L.kda_prefill_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
         L.kda_prefill_workspace_bytes.restype = C.c_size_t
+        L.kda_prefill_workspace_bytes_cuts.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+        L.kda_prefill_workspace_bytes_cuts.restype = C.c_size_t
         L.kda_prefill_launch.argtypes = [C.POINTER(KdaPrefillArgs), C.c_void_p]
         L.kda_prefill_launch.restype = C.c_int
+        L.kda_prefill_plan_counts.argtypes = [C.POINTER(KdaPrefillArgs), C.POINTER(C.c_int32), C.c_void_p]
+        L.kda_prefill_plan_counts.restype = C.c_int
         L.kda_prefill_launch_noalloc.argtypes = [C.POINTER(KdaPrefillArgs), C.c_void_p]
         L.kda_prefill_launch_noalloc.restype = C.c_int
         L.kda_segment_launch.argtypes = [C.POINTER(KdaSegmentArgs), C.c_void_p]

@@ -119,14 +119,32 @@ typedef struct KdaPrefillArgs {
                              (0 = none; nonzero: a bounded wait inside the kernel gave up, results are invalid),
                              [3] reserved; written by every call */
   int32_t kernel;         /* KDA_KERNEL_* */
+  int32_t max_cut_pieces; /* 0 (or 1): sequences are never cut.  >= 2: the device planner may cut long sequences into
+                             pieces (at most this many over the whole call) when serial chains, not the total work,
+                             bound the launch; the workspace must then be sized by kda_prefill_workspace_bytes_cuts.
+                             Function of the reference's cut plans (kda/b200/csrc/w3/base/kernel.py:389-444,482-532,
+                             kda/b200/csrc/dyn/plan_cp.cu:476-488).  Results are those of the uncut call within the
+                             tolerance of the operator (pieces start from entering states obtained through fp32 state
+                             maps); checkpoint rows, pool slots and status bits are unchanged. */
 } KdaPrefillArgs;
 
-/* Bytes of workspace a call with N sequences and H heads needs. */
+#define KDA_MAX_CUT_PIECES 128
+
+/* Bytes of workspace a call with N sequences and H heads needs (max_cut_pieces = 0). */
 size_t kda_prefill_workspace_bytes(int32_t N, int32_t H);
+/* The same with room for the state maps of `max_cut_pieces` pieces (3 x 64 KB per piece and head). */
+size_t kda_prefill_workspace_bytes_cuts(int32_t N, int32_t H, int32_t max_cut_pieces);
 
 /* Validates the caller's tables on the device, orders the (sequence, head) tasks longest first and runs the fused
- * chunk kernel.  Two kernel launches, no host read of any table. */
+ * chunk kernel.  Two kernel launches (four with max_cut_pieces >= 2: planner, chunk kernel, scan of the cut sequences'
+ * state maps, chunk kernel again), no host read of any table. */
 int kda_prefill_launch(const KdaPrefillArgs* args, void* stream);
+
+/* What the planner of the most recent kda_prefill_launch with these arguments decided (reads the workspace; this one
+ * call SYNCHRONISES the stream): counts[0] = tasks of the first launch, counts[1] = tasks of the second launch (pieces
+ * of cut sequences and the uncut sequences moved there for balance; 0 = nothing was cut), counts[2] = cut sequences.
+ * For tests and tools; the reference exposes its plan as launch.tables (kda/b200/csrc/w3/kernel.py:1218-1219). */
+int kda_prefill_plan_counts(const KdaPrefillArgs* args, int32_t* counts, void* stream);
 
 /* The same call for callers that must not allocate device memory and have no workspace to hand over: code running
  * inside a memory-pool callback or an allocator hook, a process whose device memory is fully reserved up front by a

@@ -265,6 +265,84 @@ def test_dynamic_layout_graph_replay(kda):
                 ko.check_close(ck[:C].cpu(), gold_ck, tag + " checkpoints")
 
 
+@pytest.mark.parametrize("H,lens,every,ck_dtype", [(2, [8192, 300, 64, 4000, 33], 256, torch.float32), (1, [16384], 1024, torch.bfloat16),
+                                                   (4, [6000, 6000, 100], 0, None), (8, [2048, 9000, 1, 700, 5000, 31], 64, torch.bfloat16)])
+def test_serving_call_cuts_long_requests(kda, H, lens, every, ck_dtype):
+    """With few heads a long request is a serial chain that bounds the whole launch, so the device planner cuts it into
+    pieces (affine state maps for the entering states, then the pieces as ordinary tasks).  Output, pool slots and
+    checkpoint rows must be those of the fp64 recurrence and of the same call with cutting switched off; untouched slots
+    stay bit-identical; a captured graph keeps working when the lengths change."""
+    gen = torch.Generator().manual_seed(len(lens) + H)
+    inputs = ko.make_inputs_raw(H, lens, 1200 + H)
+    q, k, v, g, beta, A_log, dt_bias, scale = to_dev(inputs[:8])
+    N, P = len(lens), len(lens) + 3
+    pool0 = (torch.randn(P, H, D, D, generator=gen) * 0.25).to(DEV)
+    idx = torch.randperm(P, generator=gen)[:N].to(torch.int32).to(DEV)
+    cu = cu_of(lens)
+    got = {}
+    for cuts in (None, 0):
+        pool = pool0.clone()
+        kw = dict(dynamic_layout=True, ssm_state_indices=idx, max_cut_pieces=cuts)
+        ck = None
+        if every:
+            ccs, rows = ck_meta(lens, every)
+            ck = torch.full((rows, H, D, D), float("nan"), device=DEV, dtype=ck_dtype)
+            kw.update(state_checkpoints=ck, checkpoint_cu_starts=ccs, checkpoint_every_n_tokens=every)
+        launch = kda.prepare(q, k, v, g, beta, A_log, dt_bias, scale, pool, cu, **kw)
+        out = launch()[0]
+        torch.cuda.synchronize()
+        assert kda.status_bits(launch) == 0 and kda.kernel_error(launch) == 0
+        na, nb, ncut = launch.plan_counts()
+        if cuts == 0:
+            assert (na, nb, ncut) == (N, 0, 0)
+        else:
+            assert ncut >= 1 and nb >= 1, f"the planner was expected to cut the long request(s): counts {(na, nb, ncut)}"
+        got[cuts] = (out.clone(), pool.clone(), None if ck is None else ck.clone())
+    gold_o, gold_s, gold_ck = gold_raw(inputs[:8], lens, init=pool0[idx.long()].cpu(), every=every)
+    tag = f"cut serving call H={H} lens={lens} every={every}"
+    ko.check_close(got[None][0].cpu(), gold_o, tag + " output")
+    ko.check_close(got[None][1][idx.long()].cpu(), gold_s, tag + " pool slots")
+    ko.check_close(got[None][0].float().cpu(), got[0][0].float().cpu(), tag + " output vs uncut call")
+    ko.check_close(got[None][1][idx.long()].cpu(), got[0][1][idx.long()].cpu(), tag + " pool slots vs uncut call")
+    keep = torch.ones(P, dtype=torch.bool, device=DEV)
+    keep[idx.long()] = False
+    assert torch.equal(got[None][1][keep], pool0[keep]), tag + ": other pool slots modified"
+    if every:
+        assert not torch.isnan(got[None][2].float()).any(), tag + ": a checkpoint row was left unwritten"
+        ko.check_close(got[None][2].float().cpu(), gold_ck, tag + " checkpoint rows")
+        ko.check_close(got[None][2].float().cpu(), got[0][2].float().cpu(), tag + " checkpoint rows vs uncut call")
+
+
+def test_cut_plan_follows_the_layout_under_one_graph(kda):
+    """One captured graph: the planner cuts when a replay's layout has a dominating long sequence and does not when the
+    same tokens come as many short ones."""
+    H, T, N = 2, 8192, 16
+    inputs = ko.make_inputs_raw(H, [T], 1300)
+    q, k, v, g, beta, A_log, dt_bias, scale = to_dev(inputs[:8])
+    pool0 = (torch.randn(N + 2, H, D, D, generator=torch.Generator().manual_seed(9)) * 0.25).to(DEV)
+    pool = pool0.clone()
+    idx = torch.arange(N, dtype=torch.int32, device=DEV)
+    layouts = [[T - (N - 1)] + [1] * (N - 1), [T // N] * N, [5000, 3000] + [16] * 12 + [0, 0]]
+    cu = cu_of(layouts[0])
+    launch = kda.prepare(q, k, v, g, beta, A_log, dt_bias, scale, pool, cu, dynamic_layout=True, ssm_state_indices=idx)
+    launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        res = launch()
+    for lens, expect_cut in zip(layouts, (True, False, True)):
+        cu.copy_(cu_of(lens))
+        pool.copy_(pool0)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert kda.status_bits(launch) == 0 and kda.kernel_error(launch) == 0
+        assert (launch.plan_counts()[2] > 0) == expect_cut, f"lens {lens[:4]}..: counts {launch.plan_counts()}"
+        gold_o, gold_s, _ = gold_raw(inputs[:8], lens, init=pool0[:N].cpu())
+        ko.check_close(res[0].cpu(), gold_o, f"graph replay with cuts, lens {lens[:4]}.. output")
+        ko.check_close(pool[:N].cpu(), gold_s, f"graph replay with cuts, lens {lens[:4]}.. pool slots")
+        assert torch.equal(pool[N:], pool0[N:])
+
+
 def test_wrapper_matches_run(kda):
     d = to_dev(ko.make_inputs_raw(12, [1000, 300, 17], 900))
     q, k, v, g, beta, A_log, dt_bias, scale, init, cu = d
