@@ -47,13 +47,13 @@ Workspace carve(void* base, int N, int H, int pieces = 0) {
   const size_t na = n + 2 * (size_t)pieces;
   w.tasks = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + na * sizeof(kda::Task), 256);
   w.tasks_unsorted = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + n * sizeof(kda::Task), 256);
-  w.n_tasks = reinterpret_cast<int*>(b + off); off = align_up(off + 16, 256);
+  w.n_tasks = reinterpret_cast<int*>(b + off); off = align_up(off + 32, 256);
   w.cu_safe = reinterpret_cast<long long*>(b + off); off = align_up(off + (n + 1) * sizeof(long long), 256);
   w.trash = reinterpret_cast<float*>(b + off); off = align_up(off + (size_t)H * kda::STATE_ELEMS * sizeof(float), 256);
   w.tasks_b = nullptr; w.chains = nullptr; w.map_P = w.map_L = w.map_E = nullptr;
   if (pieces > 0) {
     const size_t maps = (size_t)pieces * H * kda::STATE_ELEMS * sizeof(float);
-    w.tasks_b = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + (n + pieces) * sizeof(kda::Task), 256);
+    w.tasks_b = reinterpret_cast<kda::Task*>(b + off); off = align_up(off + 2 * (size_t)pieces * sizeof(kda::Task), 256);
     w.chains = reinterpret_cast<kda::ScanChain*>(b + off); off = align_up(off + ((size_t)pieces / 2 + 1) * sizeof(kda::ScanChain), 256);
     w.map_P = reinterpret_cast<float*>(b + off); off = align_up(off + maps, 256);
     w.map_L = reinterpret_cast<float*>(b + off); off = align_up(off + maps, 256);
@@ -237,7 +237,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
     if (e != cudaSuccess) return cuda_fail(e);
     p.tasks = w.tasks_b;
     p.n_tasks = w.n_tasks + 1;
-    e = umma ? kda::launch_chunk_umma(p, maps, a->N + pieces, stream) : kda::launch_chunk_fwd(p, a->N + pieces, stream);
+    e = umma ? kda::launch_chunk_umma(p, maps, 2 * pieces, stream) : kda::launch_chunk_fwd(p, 2 * pieces, stream);
     if (e != cudaSuccess) return cuda_fail(e);
   }
   return KDA_OK;

@@ -15,23 +15,22 @@
 // the MMA warp's issue path.  Because tf32 operands keep 10 mantissa bits, the state enters the products more accurately
 // than a bf16 copy would.
 //
-// The intra-chunk products kd' ki'^T and qd' ki'^T run on the tensor core as well (MMA0, ONE bf16 product straight
-// from the 128-byte-swizzled bf16 tiles the operand preparation leaves where the copy engine put q and k, which are
-// interleaved so that they read as one 64-row operand); two warps pull the two 32x32 results out of tensor memory, one
-// row per lane, mask them and invert I + diag(beta) tril(.).
-//
 // Warp roles (28 warps):
-//    0, 1   triangular inverse of alternating chunks, and the M tile of the other warp's chunks (the two products of a
-//           chunk sit in tensor-memory lane quarters 0 and 1)
-//    4      MMA issuer (+ tensor-memory allocation); the whole warp runs the issue loop on warp-uniform values
-//    5      loader: one lane polls three TMA copy streams (g / q,k / v); v goes straight into the consumer stage
-//    8-15   tensor-memory warps: state load, per-chunk decay, checkpoints, final store, and O -> bf16 -> global; each
+//    0      MMA issuer (+ tensor-memory allocation); the whole warp runs the issue loop on warp-uniform values
+//    1-2    triangular inverse, alternating chunks
+//    3      loader: one lane polls three TMA copy streams (g / q,k / v); v goes straight into the consumer stage
+//    4-11   tensor-memory warps: state load, per-chunk decay, checkpoints, final store, and O -> bf16 -> global; each
 //           warp serves half of the columns of one lane quarter
-//    2, 3, 6, 7, 16-27  operand preparation in two groups of eight warps that alternate chunks: gate + cumsum, L2
-//           norm, decayed operand tiles
+//    12-27  operand preparation in two groups of eight warps that alternate chunks: gate + cumsum, L2 norm, decayed
+//           operand tiles, intra-chunk products on mma.sync
 // Roles hand off through mbarriers; every wait is bounded (see kda_umma.cuh): on a timeout the CTA keeps its control
 // flow, waits (bounded again) for its copies and tensor-core work in flight, frees tensor memory and reports an error
 // code in status[2].
+//
+// Measured alternative, not kept: the intra-chunk products as one bf16 tcgen05.mma over interleaved q / k tiles with
+// the two results pulled out of tensor memory by the inverse warps.  It halves the work of the preparation warps, but
+// the tensor-core round trip (issue, commit, barrier, tensor-memory load) and the extraction sit on the chain
+// tiles -> products -> inverse -> MMA2, which with two operand stages is what sets the per-chunk time: 3-13 % slower.
 #include "kda_common.cuh"
 #include "kda_plan.cuh"
 #include "kda_tma.cuh"
@@ -44,43 +43,35 @@ namespace u {
 
 constexpr int WARPS = 28;
 constexpr int THREADS = WARPS * 32;
-// Warp ids.  A warp issues on scheduler id % 4 and may only touch tensor-memory lanes [32 (id % 4), +32).  The serial
-// roles (MMA issuer, inverse) share their schedulers with three operand-preparation warps instead of five.
-constexpr int W_INV_A = 0, W_INV_B = 1, W_MMA = 4, W_LOAD = 5, W_SCALE0 = 8, W_PREP_HI = 16;   // prep: 2, 3, 6, 7, 16..27
+constexpr int W_MMA = 0, W_INV0 = 1, W_LOAD = 3, W_SCALE0 = 4, W_PREP0 = 12;
 constexpr int PREP_GROUPS = 2;                 // group g prepares the chunks c with c % 2 == g, in stage g
 constexpr int PREP_WARPS = 8, PREP_THREADS = 256;   // per group
 
 // ---- shared memory map (bytes); operand tiles are 1024-byte aligned
 constexpr int CS_KDQD = 0, CS_KR = 32768, CS_V = 49152, CS_TB = 57344, CS_M = 61440, CS_STAGE = 65536;
 constexpr int OFF_CONS = 0;                                   // 2 stages
-// raw stage: the gate tile, then the q / k tiles interleaved by 64-channel half: [x h0][y h0][x h1][y h1] with
-// (x, y) = (k, q) in stage 0 and (q, k) in stage 1, 4096 bytes each.  Read as ONE 64-row K-major operand, rows 0-31
-// are x and rows 32-63 are y, so a single product with ki' yields both intra-chunk products (in different lanes).
-constexpr int RAW_G = 0, RAW_QK = 16384, RAW_STAGE = 32768;
-__device__ __forceinline__ constexpr int raw_k_off(int s) { return RAW_QK + (s ? 4096 : 0); }
-__device__ __forceinline__ constexpr int raw_q_off(int s) { return RAW_QK + (s ? 0 : 4096); }
+constexpr int RAW_G = 0, RAW_Q = 16384, RAW_K = 24576, RAW_STAGE = 32768;
 constexpr int OFF_RAW = OFF_CONS + 2 * CS_STAGE;              // 2 stages
 constexpr int OFF_KIS = OFF_RAW + 2 * RAW_STAGE;              // 2 x 8192 (one per prep group)
 constexpr int OFF_TBH = OFF_KIS + 2 * 8192;                   // 2 x 2048 (bf16, 64-byte swizzle)
 constexpr int OFF_L = OFF_TBH + 4096;                         // 2 x 4096 fp32 [32][32]
 constexpr int OFF_DEC = OFF_L + 8192;                         // 4 x 512 (a slot is rewritten four chunks later)
 constexpr int OFF_FR = OFF_DEC + 2048;                        // per prep group: r, 2^r, 2^(G31-r) : 2 x 3 x 512
-constexpr int OFF_TOTX = OFF_FR + 2 * 1536;                   // per prep group: first-half decay totals (step A exchange): 2 x 512
-constexpr int OFF_LBETA = OFF_TOTX + 1024;                    // beta next to L: 2 x 128
+constexpr int OFF_BETA = OFF_FR + 2 * 1536;                   // raw-stage beta: 2 x 128
+constexpr int OFF_LBETA = OFF_BETA + 256;                     // beta next to L: 2 x 128
 constexpr int OFF_BAR = OFF_LBETA + 256;                      // mbarriers
-constexpr int NUM_BARS = 34;
+constexpr int NUM_BARS = 32;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // +0 tmem slot, +8 abort code, +12 range flag, +16 wait limit (ns)
 constexpr int SMEM_BYTES = OFF_MISC + 64;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 // mbarrier indices
-constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_QK_FULL = 4, B_QK_EMPTY = 6, B_V_FULL = 8, B_V_EMPTY = 10, B_KDQD_EMPTY = 12,
-              B_CONS_EMPTY = 14, B_BF_FULL = 16, B_P1_FULL = 18, B_AM_FULL = 20, B_INV_FULL = 22, B_M_FULL = 24, B_O_FULL = 26,
-              B_O_EMPTY = 28, B_MMA1_DONE = 30, B_S_READY = 31, B_DRAIN = 32;
+constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
+              B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20, B_V_EMPTY = 21,
+              B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29;
 
-// tensor-memory columns: state, [W | O] x 2, U x 2, intra-chunk products x 2 (A and M of a chunk share 32 columns:
-// one in lanes 0-31, the other in lanes 32-63, swapped between the stages)
-constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256, TM_AM = 320;   // [A ; M]: 32 columns per stage
+// tensor-memory columns
+constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
 
 // error codes written to status[2] when a bounded wait gives up (which role, which barrier)
 constexpr int E_LOAD = 0x40, E_PREP = 0x80, E_INV = 0xc0, E_MMA = 0x100, E_SCALE = 0x140, E_EPI = 0x180, E_DRAIN = 0x1c0;
@@ -96,11 +87,9 @@ constexpr int E_LOAD = 0x40, E_PREP = 0x80, E_INV = 0xc0, E_MMA = 0x100, E_SCALE
 // Byte offset of element (row, col) of a raw / decayed bf16 [32][128] tile as the copy engine lays it out with the
 // 128-byte swizzle: two halves of 64 channels, each 32 rows of 128 bytes, 16-byte chunks XOR-ed with (row % 8).
 // ldmatrix phases (8 rows, one chunk) are bank-conflict free in this layout.
-__device__ __forceinline__ uint32_t tile_off(int row, int col, int half_stride) {
-  return (uint32_t)((col >> 6) * half_stride + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + ((col & 7) << 1));
+__device__ __forceinline__ uint32_t rawtile_off(int row, int col) {
+  return (uint32_t)((col >> 6) * 4096 + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + ((col & 7) << 1));
 }
-__device__ __forceinline__ uint32_t rawtile_off(int row, int col) { return tile_off(row, col, 8192); }   // q / k tiles
-__device__ __forceinline__ uint32_t kistile_off(int row, int col) { return tile_off(row, col, 4096); }   // ki' tile
 
 #ifndef KDA_SLEEP_NS
 #define KDA_SLEEP_NS 32
@@ -137,10 +126,10 @@ struct Ctx {
 template <int FE>
 __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
   // Three independent copy streams (g; q and k; v), each with its own full / empty barrier pair per stage: the gate
-  // tile is free after step B of the chunk two back, q / k once MMA0 has read them, v only once MMA2 has.  ONE lane
+  // tile is free after step B of the chunk two back, q / k after step C, v only once MMA2 has read it.  ONE lane
   // serves all three by polling the empty barriers without blocking: a blocking wait of one stream (or of a second
   // lane of this warp, which shares the warp's single scheduling slot) would delay the refill of the others by its
-  // suspend time, and the refill latency of q / k sits on the chain  copy -> step B -> MMA0 -> inverse -> MMA2.
+  // suspend time, and the refill latency of q / k sits on the chain  copy -> step B -> step C -> inverse -> MMA2.
   if (lane != 0) return;
   const int n = x.nchunks;
   int cg = 0, cq = 0, cv = 0;                 // next chunk of each stream
@@ -155,13 +144,13 @@ __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x
       const int s = cq & 1;
       if (mbar_test_wait(x.bar(B_QK_EMPTY + s), (uint32_t)(((cq >> 1) & 1) ^ 1))) {
         uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-        const uint32_t qraw = smem_u32(raw + raw_q_off(s)), kraw = smem_u32(raw + raw_k_off(s));
+        const uint32_t qraw = smem_u32(raw + RAW_Q), kraw = smem_u32(raw + RAW_K);
         const int tok0 = (int)(x.t0 + (long long)cq * C);
         tma::mbar_arrive_expect_tx(x.bar(B_QK_FULL + s), 2u * 8192u);
         tma::load_3d(qraw, &m.q, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-        tma::load_3d(qraw + 8192, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+        tma::load_3d(qraw + 4096, &m.q, 64, x.h, tok0, x.bar(B_QK_FULL + s));
         tma::load_3d(kraw, &m.k, 0, x.h, tok0, x.bar(B_QK_FULL + s));
-        tma::load_3d(kraw + 8192, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
+        tma::load_3d(kraw + 4096, &m.k, 64, x.h, tok0, x.bar(B_QK_FULL + s));
         cq++;
         progressed = true;
       }
@@ -231,8 +220,6 @@ __device__ __forceinline__ float load_beta(const ChunkParams& p, const Ctx& x, i
 }
 
 // ------------------------------------------------------------------------------------------------ prep warps
-// A group of eight warps prepares every second chunk.  Only step A needs the whole group in step (channel-owning
-// threads hand the cumulative gates to token-owning warps); after that each warp publishes its own rows.
 template <int FE>
 __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid) {
   const int pw = ptid >> 5, lane = ptid & 31;
@@ -247,14 +234,13 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
   float* fr = reinterpret_cast<float*>(x.smem + OFF_FR) + grp * 3 * D;
   float* fer = fr + D;
   float* tot = fr + 2 * D;
-  float* totx = reinterpret_cast<float*>(x.smem + OFF_TOTX) + grp * D;
-  volatile int* range_flag = reinterpret_cast<volatile int*>(x.smem + OFF_MISC + 12);
   uint8_t* raw = x.smem + OFF_RAW + s * RAW_STAGE;
-  uint8_t* rawq = raw + raw_q_off(s);
-  uint8_t* rawk = raw + raw_k_off(s);
   uint8_t* cons = x.smem + OFF_CONS + s * CS_STAGE;
   uint8_t* kis_tile = x.smem + OFF_KIS + grp * 8192;
   float* Gsm = reinterpret_cast<float*>(raw + RAW_G);
+  float* beta_s = reinterpret_cast<float*>(x.smem + OFF_BETA) + s * 32;
+  volatile int* range_flag = reinterpret_cast<volatile int*>(x.smem + OFF_MISC + 12);
+  float beta_next = (ptid < C && grp < x.nchunks) ? load_beta<FE>(p, x, grp, ptid) : 0.0f;   // one own chunk ahead
 #pragma unroll 1
   for (int c = grp; c < x.nchunks; c += PREP_GROUPS) {
     const uint32_t par = (uint32_t)((c >> 1) & 1);
@@ -264,8 +250,8 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     PROF_BEGIN;
 
     // ---- A: gate activation + inclusive cumulative log2-decay; two threads per channel, 16 tokens each.
-    // Touches only prep-private scratch (the decay slot c & 3 was last read four chunks ago, and the group has since
-    // waited for the tensor core to finish with that chunk), so it runs while the tensor core works on older chunks.
+    // Touches only prep-private scratch (the decay slot c & 3 was last read four chunks ago), so it runs while the
+    // tensor core still works on older chunks.
     {
       float a[16];
       if (FE == 1) {
@@ -290,14 +276,17 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
       // ones belong to token 0 (first half) and token 31 (second half).  Beyond 2^126 they are clamped below and the
       // intra-chunk products of this chunk are no longer exact: report it.
       if (half == 0 ? (a[0] - a[15] > 126.0f) : (a[15] < -126.0f)) *range_flag = 1;
-      if (half == 0) totx[ch] = a[15];
+      if (half == 0) tot[ch] = a[15];
       PROF_STAMP(2, 10);
-      named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place;
-                                              // every warp of the group has left step B of the previous chunk, so the
-                                              // per-channel factors below may be replaced
+      named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
       PROF_STAMP(2, 11);
+      // Every warp of the group has left the previous chunk (step C reads beta_s), so beta may be replaced only now.
+      if (ptid < C) {
+        beta_s[ptid] = beta_next;
+        if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
+      }
       if (half == 1) {
-        const float r = totx[ch];
+        const float r = tot[ch];
 #pragma unroll
         for (int i = 0; i < 16; i++) a[i] += r;
         fr[ch] = r;
@@ -313,8 +302,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     PROF_STAMP(2, 26);
 
     // ---- B: L2 norm and decayed operand tiles; a warp owns 4 tokens, a lane 4 channels.  [kd ; qd] is written as
-    // soon as MMA1 of the chunk two back has read the stage (which also means MMA0 of that chunk has read the bf16
-    // tiles); kr waits in registers until MMA3 has released the rest.
+    // soon as MMA1 of the chunk two back has read the stage; kr waits in registers until MMA3 has released the rest.
     x.wait(B_QK_FULL + s, par, E_PREP);
     x.wait(B_KDQD_EMPTY + s, par ^ 1, E_PREP);
     PROF_STAMP(2, 14);
@@ -330,8 +318,8 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
       for (int tt = 0; tt < 4; tt++) {
         const int tok = 4 * pw + tt;
         const uint32_t off = rawtile_off(tok, 4 * lane);
-        uint2 q2 = *reinterpret_cast<const uint2*>(rawq + off);
-        uint2 k2 = *reinterpret_cast<const uint2*>(rawk + off);
+        uint2 q2 = *reinterpret_cast<const uint2*>(raw + RAW_Q + off);
+        uint2 k2 = *reinterpret_cast<const uint2*>(raw + RAW_K + off);
         if (tok >= nvalid) { q2 = make_uint2(0u, 0u); k2 = make_uint2(0u, 0u); }   // rows of the next sequence
         const float qf[4] = {bf16_lo(q2.x), bf16_hi(q2.x), bf16_lo(q2.y), bf16_hi(q2.y)};
         const float kf[4] = {bf16_lo(k2.x), bf16_hi(k2.x), bf16_lo(k2.y), bf16_hi(k2.y)};
@@ -364,149 +352,119 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
           kds[j] = kd2.x; kds[j + 1] = kd2.y; qds[j] = qd2.x; qds[j + 1] = qd2.y; kis[j] = ki2.x; kis[j + 1] = ki2.y;
           kdt[j] = kt2.x; kdt[j + 1] = kt2.y; qdt[j] = qt2.x; qdt[j + 1] = qt2.y; krr[tt][j] = kr2.x; krr[tt][j + 1] = kr2.y;
         }
-        // in place: the decayed bf16 tiles of the intra-chunk products replace the raw q / k tiles (same 128-byte
-        // swizzle, which is the tensor core's K-major operand layout)
-        *reinterpret_cast<uint2*>(rawk + off) = make_uint2(pack_bf16(kds[0], kds[1]), pack_bf16(kds[2], kds[3]));
-        *reinterpret_cast<uint2*>(rawq + off) = make_uint2(pack_bf16(qds[0], qds[1]), pack_bf16(qds[2], qds[3]));
-        *reinterpret_cast<uint2*>(kis_tile + kistile_off(tok, 4 * lane)) = make_uint2(pack_bf16(kis[0], kis[1]), pack_bf16(kis[2], kis[3]));
+        // in place: the decayed bf16 tiles of the intra-chunk products replace the raw q / k tiles
+        *reinterpret_cast<uint2*>(raw + RAW_K + off) = make_uint2(pack_bf16(kds[0], kds[1]), pack_bf16(kds[2], kds[3]));
+        *reinterpret_cast<uint2*>(raw + RAW_Q + off) = make_uint2(pack_bf16(qds[0], qds[1]), pack_bf16(qds[2], qds[3]));
+        *reinterpret_cast<uint2*>(kis_tile + off) = make_uint2(pack_bf16(kis[0], kis[1]), pack_bf16(kis[2], kis[3]));
         // tf32 operands of the state products: [kd ; qd] K-major (row = token, 32 + token), kr MN-major
         *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(tok, 4 * lane, 8192)) = make_float4(kdt[0], kdt[1], kdt[2], kdt[3]);
         *reinterpret_cast<float4*>(cons + CS_KDQD + kmajor_f32_off(32 + tok, 4 * lane, 8192)) = make_float4(qdt[0], qdt[1], qdt[2], qdt[3]);
       }
     }
     PROF_STAMP(2, 27);
-    fence_proxy_async();                         // this thread's tile writes (and its reads of the g region) are ordered
-    __syncwarp();                                // before the tensor core's reads / the refill of the gate tile
-    if (lane == 0) {
-      mbar_arrive(x.bar(B_BF_FULL + s));         // this warp's rows of kd', qd', ki' (and [kd ; qd]) are in place
-      mbar_arrive(x.bar(B_G_EMPTY + s));         // ... and it no longer reads the gate tile
-    }
+    fence_proxy_async();                                  // this thread's reads / writes of the g region precede its refill
+    named_bar_sync(bar_id, PREP_THREADS);
+    if (lane == 0) mbar_arrive(x.bar(B_G_EMPTY + s));     // the gate tile may be refilled: step C does not read it
     PROF_STAMP(2, 28);
-    // ---- D: the kr operand of MMA3 goes out once the tensor core has released the rest of the stage
-    x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
-    PROF_STAMP(2, 17);
+
+    // ---- C: one 16x16 block of A = kd' ki'^T (warps 0-3) or M = qd' ki'^T (warps 4-7) per warp
+    {
+      const int which = pw >> 2, rb = (pw >> 1) & 1, cb = pw & 1;
+      const int g = lane >> 2, t = lane & 3;
+      const int i0 = 16 * rb + g, i1 = i0 + 8;
+      float acc[2][4];
 #pragma unroll
-    for (int tt = 0; tt < 4; tt++)
-      *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, 4 * pw + tt, 512, 2048)) =
-          make_float4(krr[tt][0], krr[tt][1], krr[tt][2], krr[tt][3]);
+      for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+      if (!(rb == 0 && cb == 1)) {
+        const uint32_t a_tile = smem_u32(raw + (which ? RAW_Q : RAW_K));
+        const uint32_t b_tile = smem_u32(kis_tile);
+        const int a_row = 16 * rb + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int b_row = 16 * cb + 8 * (lane >> 4) + (lane & 7);
+#pragma unroll
+        for (int kt = 0; kt < 8; kt++) {
+          uint32_t a[4], b[4];
+          ldmatrix_x4(a, a_tile + rawtile_off(a_row, (2 * kt + (lane >> 4)) * 8));
+          ldmatrix_x4(b, b_tile + rawtile_off(b_row, (2 * kt + ((lane >> 3) & 1)) * 8));
+          mma_bf16(acc[0], a, b[0], b[1]);
+          mma_bf16(acc[1], a, b[2], b[3]);
+        }
+      }
+      PROF_STAMP(2, 15);
+      if (which == 0) {
+        x.wait(B_L_EMPTY + s, par ^ 1, E_PREP);
+        float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
+        const float b0 = beta_s[i0], b1 = beta_s[i1];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const int j = 16 * cb + 8 * nt + 2 * t;
+          *reinterpret_cast<float2*>(Lsm + i0 * C + j) = make_float2((j < i0) ? acc[nt][0] * b0 : 0.0f, (j + 1 < i0) ? acc[nt][1] * b0 : 0.0f);
+          *reinterpret_cast<float2*>(Lsm + i1 * C + j) = make_float2((j < i1) ? acc[nt][2] * b1 : 0.0f, (j + 1 < i1) ? acc[nt][3] * b1 : 0.0f);
+        }
+        if (pw == 0) reinterpret_cast<float*>(x.smem + OFF_LBETA)[s * 32 + lane] = beta_s[lane];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x.bar(B_L_FULL + s));      // the inverse of this chunk may start
+      }
+      PROF_STAMP(2, 16);
+      // ---- D: the operands of MMA3 go out once the tensor core has released the rest of the stage
+      x.wait(B_CONS_EMPTY + s, par ^ 1, E_PREP);
+      PROF_STAMP(2, 17);
+#pragma unroll
+      for (int tt = 0; tt < 4; tt++)
+        *reinterpret_cast<float4*>(cons + CS_KR + mnmajor_f32_off(4 * lane, 4 * pw + tt, 512, 2048)) =
+            make_float4(krr[tt][0], krr[tt][1], krr[tt][2], krr[tt][3]);
+      if (which == 1) {
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const int j = 16 * cb + 8 * nt + 2 * t;
+          *reinterpret_cast<float2*>(cons + CS_M + kmajor_f32_off(i0, j, 0)) =
+              make_float2((j <= i0) ? acc[nt][0] : 0.0f, (j + 1 <= i0) ? acc[nt][1] : 0.0f);
+          *reinterpret_cast<float2*>(cons + CS_M + kmajor_f32_off(i1, j, 0)) =
+              make_float2((j <= i1) ? acc[nt][2] : 0.0f, (j + 1 <= i1) ? acc[nt][3] : 0.0f);
+        }
+      }
+    }
     PROF_STAMP(2, 29);
     fence_proxy_async();
     __syncwarp();
-    if (lane == 0) mbar_arrive(x.bar(B_P1_FULL + s));
+    if (lane == 0) {
+      mbar_arrive(x.bar(B_P1_FULL + s));
+      mbar_arrive(x.bar(B_QK_EMPTY + s));        // the q / k tiles are no longer read
+    }
   }
 }
 
-// ------------------------------------------------------------------------------------------------ MMA0
-// MMA0 of chunk cc: [x ; y] ki'^T with (x, y) = (kd', qd') in stage 0 and (qd', kd') in stage 1, ONE bf16 product with
-// N = 32, K = 128.  The 64 token rows of the interleaved q / k tiles are the first rows of an M = 128 operand; rows
-// 64-127 of the result (whatever lies behind the tiles in shared memory) land in tensor-memory lanes 64-127 of the
-// product columns, which nothing reads.
-__device__ __forceinline__ void issue_mma0(const Ctx& x, uint64_t d_xy, uint64_t d_ki, uint32_t tmem, int cc, uint32_t go) {
-  constexpr uint32_t ID0 = make_idesc(FMT_BF16, 128, 32, 0, 0, 0);
-  const int s2 = cc & 1;
-  tc_fence_after();
-  mma0_block(tmem + TM_AM + 32 * s2, (uint32_t)d_xy + (uint32_t)(s2 * (RAW_STAGE >> 4)), (uint32_t)(d_xy >> 32),
-             (uint32_t)d_ki + (uint32_t)(s2 * (8192 >> 4)), (uint32_t)(d_ki >> 32), ID0, go);
-  mma_commit_pred(x.bar(B_AM_FULL + s2), go);           // both inverse warps may fetch the products
-  mma_commit_pred(x.bar(B_QK_EMPTY + s2), go);          // the q / k tiles may be refilled
-}
-
 // ------------------------------------------------------------------------------------------------ inverse warps
-// MMA0 leaves both intra-chunk products of a chunk in 32 tensor-memory columns: kd' ki'^T in one lane quarter and
-// qd' ki'^T in the next (which is which alternates with the stage, see the raw stage layout).  Two warps, one per
-// quarter, take them out, one row per lane: for the chunks of its own parity a warp does
-//   L = diag(beta) tril(kd' ki'^T, -1)  ->  T = (I + L)^-1  ->  Tb = T diag(beta)   (tf32 and bf16 tiles for MMA2)
-// and for the other chunks only
-//   M = tril(qd' ki'^T)                                                            (tf32 tile for the O part of MMA3)
-// T is computed in the warp's private fp32 [32][32] buffer, in place:
+// T = (I + L)^-1 for the strictly lower triangular fp32 L [32][32] of a chunk, in place in L's buffer, by one warp:
 //   1. the two 16x16 diagonal blocks by forward substitution in fp32 registers, one half-warp per block, lane = column
 //      (16 dependent rows instead of 32);
 //   2. the off-diagonal block T10 = -T11 (L10 T00) as two 16x16x16 products on mma.sync (tf32 operands, fp32
 //      accumulation; T is consumed as a tf32 / bf16 tensor-core operand anyway).
-// The buffer's 16-byte pieces are XOR-ed with (row % 8), so that row-per-lane vector accesses and the fragment reads of
-// the products spread over the banks.
-__device__ __forceinline__ int lidx(int row, int col) { return row * C + ((((col >> 2) ^ (row & 7)) << 2) | (col & 3)); }
-
-// acc[nt] (16 x 8) += A * B for the 16x16 blocks of the buffer whose top-left elements are (RA, CA) and (RB, CB)
-template <int RA, int CA, int RB, int CB>
-__device__ __forceinline__ void mm16_tf32(float (&acc)[2][4], const float* L, int g, int t) {
-  // (RA + g) % 8 == (RA + g + 8) % 8 == g and (RB + 8 kt + t [+ 4]) % 8 == t [+ 4]: the swizzle terms are the lane's own
+// Then Tb = T diag(beta) goes out as the tf32 and bf16 operand tiles of MMA2.
+__device__ __forceinline__ void mm16_tf32(float (&acc)[2][4], const float* A, const float* B, int lane) {
+  // acc[nt] (16 x 8) += A[16][16] * B[16][16], both row-major with a row stride of 32 floats
+  const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int kt = 0; kt < 2; kt++) {
-    const float* ar = L + (RA + g) * C;
-    const int ca0 = ((((CA + 8 * kt) >> 2) ^ g) << 2) | t, ca1 = ((((CA + 8 * kt + 4) >> 2) ^ g) << 2) | t;
-    const uint32_t a[4] = {__float_as_uint(ar[ca0]), __float_as_uint(ar[8 * C + ca0]), __float_as_uint(ar[ca1]), __float_as_uint(ar[8 * C + ca1])};
-    const float* b0 = L + (RB + 8 * kt + t) * C;
-    const float* b1 = b0 + 4 * C;
+    const uint32_t a[4] = {__float_as_uint(A[g * C + 8 * kt + t]), __float_as_uint(A[(g + 8) * C + 8 * kt + t]),
+                           __float_as_uint(A[g * C + 8 * kt + t + 4]), __float_as_uint(A[(g + 8) * C + 8 * kt + t + 4])};
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++) {
-      const int cb = CB + 8 * nt + g;
-      mma_tf32(acc[nt], a, __float_as_uint(b0[(((cb >> 2) ^ t) << 2) | (cb & 3)]), __float_as_uint(b1[(((cb >> 2) ^ (t + 4)) << 2) | (cb & 3)]));
-    }
+    for (int nt = 0; nt < 2; nt++)
+      mma_tf32(acc[nt], a, __float_as_uint(B[(8 * kt + t) * C + 8 * nt + g]), __float_as_uint(B[(8 * kt + t + 4) * C + 8 * nt + g]));
   }
 }
 
-template <int FE>
-__device__ void role_inverse(const ChunkParams& p, const Ctx& x, uint32_t tmem, int which, int lane) {
+__device__ void role_inverse(const Ctx& x, int which, int lane) {
   const int blk = lane >> 4, cl = lane & 15;
   const int g = lane >> 2, t = lane & 3;
-  // the inverse of the chunks with c % 2 == which lives in stage `which`
-  float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + which * 1024;
-  float* lbeta = reinterpret_cast<float*>(x.smem + OFF_LBETA) + which * 32;
-  uint8_t* cons_own = x.smem + OFF_CONS + which * CS_STAGE;
-  uint8_t* tbh = x.smem + OFF_TBH + which * 2048;
-  const uint32_t tq = tmem + TM_AM + ((uint32_t)(32 * which) << 16);      // this warp's lane quarter (its id % 4 == which)
-  float beta_next = which < x.nchunks ? load_beta<FE>(p, x, which, lane) : 0.0f;   // one own chunk ahead
-  const uint32_t go = elect_one();
-  const uint32_t sb = smem_u32(x.smem);
-  const uint64_t d_xy = make_sdesc(sb + OFF_RAW + RAW_QK, 16, 1024, LAYOUT_SW128);
-  const uint64_t d_ki = make_sdesc(sb + OFF_KIS, 16, 1024, LAYOUT_SW128);
-  // Row `b0 + i` of a diagonal block, columns of the same block: the 16-byte piece index (4 blk + j / 4) ^ (i % 8)
-  // splits into a part that only depends on (blk, i & 4) and a compile-time part, so two base pointers serve all rows.
-  const float* Ld0 = Lsm + (16 * blk) * C + ((4 * blk) << 2);
-  const float* Ld1 = Lsm + (16 * blk) * C + (((4 * blk) ^ 4) << 2);
 #pragma unroll 1
-  for (int c = 0; c < x.nchunks; c++) {
+  for (int c = which; c < x.nchunks; c += 2) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
-    if (s != which) {
-      // ---- M = tril(qd' ki'^T) of the other warp's chunk: row `lane`, 16 columns at a time
-      uint8_t* mt = x.smem + OFF_CONS + s * CS_STAGE + CS_M;
-      x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);           // MMA3 of the chunk two back has read M
-      x.wait(B_AM_FULL + s, par, E_INV);
-      tc_fence_after();
-      PROF_BEGIN;
-#pragma unroll
-      for (int hb = 0; hb < 2; hb++) {
-        uint32_t r[16];
-        tmem_ld16(tq + 32 * s + 16 * hb, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j4 = 0; j4 < 4; j4++) {
-          const int j = 16 * hb + 4 * j4;
-          float4 f;
-          f.x = (j + 0 <= lane) ? __uint_as_float(r[4 * j4 + 0]) : 0.0f;
-          f.y = (j + 1 <= lane) ? __uint_as_float(r[4 * j4 + 1]) : 0.0f;
-          f.z = (j + 2 <= lane) ? __uint_as_float(r[4 * j4 + 2]) : 0.0f;
-          f.w = (j + 3 <= lane) ? __uint_as_float(r[4 * j4 + 3]) : 0.0f;
-          *reinterpret_cast<float4*>(mt + kmajor_f32_off(lane, j, 0)) = f;
-        }
-      }
-      tc_fence_before();                                   // the next MMA0 of this stage may overwrite the products
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(x.bar(B_M_FULL + s));
-      PROF_STAMP(3, 28);
-      continue;
-    }
-    // ---- own chunk.  This warp issues MMA0 itself, the moment the operand preparation has published the bf16 tiles
-    // (the products head the longest chain of the chunk: MMA0 -> inverse -> MMA2), all lanes convergent with one
-    // elected lane issuing.  The products of the chunk two back have been fetched: by this warp in program order, by
-    // the other inverse warp as its M_FULL arrival tells.
-    x.wait(B_BF_FULL + s, par, E_INV);
-    if (c >= 2) x.wait(B_M_FULL + s, par ^ 1, E_INV);
-    issue_mma0(x, d_xy, d_ki, tmem, c, go);
-    // Everything that does not depend on the products comes next, while the warp would only wait.
+    // Everything that does not depend on this chunk's L comes first, while the warp would only wait for L anyway (the
+    // v tile and the release of the stage by MMA3 of the chunk two back are normally long there): after the inversion
+    // only the operand write-out remains between L and MMA2.
     // The v tile of a partial last chunk holds another sequence's rows (or worse) past the end of the run: zero them
     // so that they cannot poison MMA2 (their Tb columns are zero, but 0 * NaN is NaN).  This warp observes every
     // phase of the v barrier of its stage, so the wait cannot be satisfied by an older phase, and MMA2 waits for this
@@ -515,106 +473,79 @@ __device__ void role_inverse(const ChunkParams& p, const Ctx& x, uint32_t tmem, 
     {
       const int nvalid = min(C, x.len - c * C);
       if (nvalid < C) {
-        uint8_t* vt = cons_own + CS_V;
+        uint8_t* vt = x.smem + OFF_CONS + s * CS_STAGE + CS_V;
         for (int i = lane; i < (C - nvalid) * 16; i += 32) {     // whole 128-byte lines of both 64-channel halves
           const int row = nvalid + (i >> 4), piece = i & 15;
           *reinterpret_cast<uint4*>(vt + (piece >> 3) * 4096 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
     }
-    const float beta = beta_next;                         // 0 for rows past the end of the run
-    if (c + 2 < x.nchunks) beta_next = load_beta<FE>(p, x, c + 2, lane);
-    x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);             // MMA2 of the chunk two back has read Tb
-    x.wait(B_AM_FULL + s, par, E_INV);
-    tc_fence_after();
+    x.wait(B_CONS_EMPTY + s, par ^ 1, E_INV);
+    x.wait(B_L_FULL + s, par, E_INV);
+    float* Lsm = reinterpret_cast<float*>(x.smem + OFF_L) + s * 1024;
     PROF_BEGIN;
-    // row `lane` of kd' ki'^T, scaled by the row's beta -> row of the buffer, 16 columns at a time.  No triangular mask
-    // is needed: the substitution reads only the strictly lower part of a diagonal block and then overwrites the whole
-    // block, the (1,0) block is all below the diagonal, and the (0,1) block (rows 0-15, columns 16-31) is zeroed here.
-#pragma unroll
-    for (int hb = 0; hb < 2; hb++) {
-      uint32_t r[16];
-      tmem_ld16(tq + 32 * s + 16 * hb, r);
-      tmem_wait_ld();
-      const bool zero = hb == 1 && lane < 16;      // a select, not a product with 0: the products above the diagonal
-                                                   // pair a grown factor with a grown one and may be infinite
-#pragma unroll
-      for (int j4 = 0; j4 < 4; j4++) {
-        const int j = 16 * hb + 4 * j4;
-        float4 f = make_float4(__uint_as_float(r[4 * j4 + 0]) * beta, __uint_as_float(r[4 * j4 + 1]) * beta,
-                               __uint_as_float(r[4 * j4 + 2]) * beta, __uint_as_float(r[4 * j4 + 3]) * beta);
-        if (zero) f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        *reinterpret_cast<float4*>(Lsm + lane * C + (((j >> 2) ^ (lane & 7)) << 2)) = f;
-      }
-    }
-    tc_fence_before();                                     // (the products are not read again)
-    lbeta[lane] = beta;
-    __syncwarp();
-    PROF_STAMP(3, 25);
     // ---- 1: diagonal blocks
     {
+      const float* Lb = Lsm + blk * 16 * C + blk * 16;
       float Tc[16];
 #pragma unroll
       for (int i = 0; i < 16; i++) {
-        const float* Lr = ((i & 4) ? Ld1 : Ld0) + i * C;          // row 16 blk + i; piece j / 4 sits at (j / 4) ^ (i & 3)
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
         for (int j = 0; j + 3 < i; j += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(Lr + (((j >> 2) ^ (i & 3)) << 2));
+          const float4 l4 = *reinterpret_cast<const float4*>(Lb + i * C + j);
           a0 = fmaf(l4.x, Tc[j], a0);
           a1 = fmaf(l4.y, Tc[j + 1], a1);
           a2 = fmaf(l4.z, Tc[j + 2], a2);
           a3 = fmaf(l4.w, Tc[j + 3], a3);
         }
 #pragma unroll
-        for (int j = i & ~3; j < i; j++) a0 = fmaf(Lr[(((j >> 2) ^ (i & 3)) << 2) | (j & 3)], Tc[j], a0);
+        for (int j = i & ~3; j < i; j++) a0 = fmaf(Lb[i * C + j], Tc[j], a0);
         Tc[i] = ((i == cl) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
       }
       __syncwarp();                                   // every lane has read its diagonal block
+      float* Tb_ = Lsm + blk * 16 * C + blk * 16;
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
-        float* Lr = const_cast<float*>(((i & 4) ? Ld1 : Ld0) + i * C);
-        Lr[((((cl >> 2)) ^ (i & 3)) << 2) | (cl & 3)] = Tc[i];
-      }
+      for (int i = 0; i < 16; i++) Tb_[i * C + cl] = Tc[i];
     }
     __syncwarp();
     // ---- 2: T10 = -T11 (L10 T00), in place in the (1,0) block
     {
+      float* L10 = Lsm + 16 * C;
       float acc[2][4];
 #pragma unroll
       for (int i = 0; i < 2; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
-      mm16_tf32<16, 0, 0, 0>(acc, Lsm, g, t);         // X = L10 T00
+      mm16_tf32(acc, L10, Lsm, lane);                 // X = L10 T00
       __syncwarp();                                   // L10 fully read
-      // rows 16 + g and 24 + g (both % 8 == g), columns 8 nt + 2 t
-      float* x0 = Lsm + (16 + g) * C;
 #pragma unroll
       for (int nt = 0; nt < 2; nt++) {
-        const int cc = ((((8 * nt + 2 * t) >> 2) ^ g) << 2) | ((2 * t) & 3);
-        *reinterpret_cast<float2*>(x0 + cc) = make_float2(acc[nt][0], acc[nt][1]);
-        *reinterpret_cast<float2*>(x0 + 8 * C + cc) = make_float2(acc[nt][2], acc[nt][3]);
+        *reinterpret_cast<float2*>(L10 + g * C + 8 * nt + 2 * t) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(L10 + (g + 8) * C + 8 * nt + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
         acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
       }
       __syncwarp();
-      mm16_tf32<16, 16, 16, 0>(acc, Lsm, g, t);       // T11 X
+      mm16_tf32(acc, Lsm + 16 * C + 16, L10, lane);   // T11 X
       __syncwarp();                                   // X fully read
 #pragma unroll
       for (int nt = 0; nt < 2; nt++) {
-        const int cc = ((((8 * nt + 2 * t) >> 2) ^ g) << 2) | ((2 * t) & 3);
-        *reinterpret_cast<float2*>(x0 + cc) = make_float2(-acc[nt][0], -acc[nt][1]);
-        *reinterpret_cast<float2*>(x0 + 8 * C + cc) = make_float2(-acc[nt][2], -acc[nt][3]);
+        *reinterpret_cast<float2*>(L10 + g * C + 8 * nt + 2 * t) = make_float2(-acc[nt][0], -acc[nt][1]);
+        *reinterpret_cast<float2*>(L10 + (g + 8) * C + 8 * nt + 2 * t) = make_float2(-acc[nt][2], -acc[nt][3]);
       }
     }
     __syncwarp();
+    const float* lbeta = reinterpret_cast<const float*>(x.smem + OFF_LBETA) + s * 32;
     PROF_STAMP(3, 26);
-    uint8_t* tb = cons_own + CS_TB;
-    // Tb = T diag(beta): lane = row; eight columns (one 16-byte bf16 chunk, two 16-byte tf32 chunks) per step
+    uint8_t* tb = x.smem + OFF_CONS + s * CS_STAGE + CS_TB;
+    uint8_t* tbh = x.smem + OFF_TBH + s * 2048;
+    // Tb = T diag(beta): lane = row; eight columns (one 16-byte bf16 chunk, two 16-byte tf32 chunks) per step, the
+    // column group rotated by the lane so that the wide loads and stores of a quarter-warp spread over the banks.
 #pragma unroll
     for (int jj = 0; jj < 4; jj++) {
-      const int c0 = 8 * jj;
-      const float4 ta = *reinterpret_cast<const float4*>(Lsm + lane * C + (((2 * jj) ^ (lane & 7)) << 2));
-      const float4 tc = *reinterpret_cast<const float4*>(Lsm + lane * C + (((2 * jj + 1) ^ (lane & 7)) << 2));
+      const int c0 = 8 * ((jj + lane) & 3);
+      const float4 ta = *reinterpret_cast<const float4*>(Lsm + lane * C + c0);
+      const float4 tc = *reinterpret_cast<const float4*>(Lsm + lane * C + c0 + 4);
       const float4 ba = *reinterpret_cast<const float4*>(lbeta + c0);
       const float4 bb = *reinterpret_cast<const float4*>(lbeta + c0 + 4);
       const float4 va = make_float4(ta.x * ba.x, ta.y * ba.y, ta.z * ba.z, ta.w * ba.w);
@@ -626,22 +557,17 @@ __device__ void role_inverse(const ChunkParams& p, const Ctx& x, uint32_t tmem, 
     }
     fence_proxy_async();
     __syncwarp();
-    if (lane == 0) mbar_arrive(x.bar(B_INV_FULL + s));
-    PROF_STAMP(3, 27);
-  }
-  // The last MMA0 this warp issued has retired before the CTA leaves (on the normal path the warp waited for it long
-  // ago; after a give-up elsewhere this keeps the tensor core from writing freed tensor memory).
-  if (which < x.nchunks) {
-    const int cl = ((x.nchunks - 1 - which) & ~1) + which;
-    if (!mbar_wait_drain(x.bar(B_AM_FULL + which), (uint32_t)((cl >> 1) & 1), x.abort_flag))
-      atomicCAS(const_cast<int*>(x.abort_flag), 0, E_DRAIN + B_AM_FULL);
+    if (lane == 0) {
+      mbar_arrive(x.bar(B_INV_FULL + s));
+      mbar_arrive(x.bar(B_L_EMPTY + s));
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------------ MMA issuer
-// Runs on ALL lanes of one warp with warp-uniform values only; one elected lane issues the tensor-core instructions
+// Runs on ALL lanes of warp 0 with warp-uniform values only; one elected lane issues the tensor-core instructions
 // (predicated inside the asm).  Keeping the control flow convergent lets the compiler hold descriptors, tensor-memory
-// addresses and barrier addresses in uniform registers, which is what makes issuing ~34 small MMAs per chunk cheap.  (MMA0 is issued by the inverse warps.)
+// addresses and barrier addresses in uniform registers, which is what makes issuing ~34 small MMAs per chunk cheap.
 __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
   const uint32_t go = elect_one();
   const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_any, 0);
@@ -667,8 +593,8 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
   for (int c = 0; c < nchunks; c++) {
     const int s = c & 1;
     const uint32_t par = (uint32_t)((c >> 1) & 1);
-    const uint32_t so = (uint32_t)(s * (CS_STAGE >> 4));          // stage offset in the start-address field
-    const uint32_t so_tbh = (uint32_t)(s * (2048 >> 4));
+    const uint64_t so = (uint64_t)(s * (CS_STAGE >> 4));          // stage offset in the start-address field
+    const uint64_t so_tbh = (uint64_t)(s * (2048 >> 4));
     const uint32_t tWO = tmem + TM_WO + 64 * s;
     const uint32_t tU = tmem + TM_U + 32 * s;             // U alternates too: MMA2 of the next chunk never overwrites
                                                           // columns that MMA3 of this chunk may still be reading
@@ -676,25 +602,34 @@ __device__ void role_mma(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
     x.wait(B_O_EMPTY + s, par ^ 1, E_MMA, 0);
     tc_fence_after();
     PROF_BEGIN;
-    mma1_block(tWO, tS, (uint32_t)d_kdqd + so, (uint32_t)(d_kdqd >> 32), ID1, go);
+#pragma unroll
+    for (int ks = 0; ks < 16; ks++)
+      mma_ts_tf32_pred(tWO, tS + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
     mma_commit_pred(x.bar(B_MMA1_DONE), go);              // the tensor-memory warps may rescale the state
     mma_commit_pred(x.bar(B_KDQD_EMPTY + s), go);         // [kd ; qd] of this stage may be rewritten
     PROF_STAMP(4, 26);
     x.wait(B_INV_FULL + s, par, E_MMA, 0);
     x.wait(B_V_FULL + s, par, E_MMA, 0);
     tc_fence_after();
-    if (!v_zero)
-      mma2a_block(tU, (uint32_t)d_v + so, (uint32_t)(d_v >> 32), (uint32_t)d_tbh + so_tbh, (uint32_t)(d_tbh >> 32), ID2A, go);
-    mma_ts4_block(tU, tWO, (uint32_t)d_tb + so, (uint32_t)(d_tb >> 32), ID2B, go, v_zero ? 0u : 1u);
+    if (!v_zero) {
+#pragma unroll
+      for (int ks = 0; ks < 2; ks++)
+        mma_ss_f16_pred(tU, d_v + so + (uint64_t)((2 * ks * 1024) >> 4), d_tbh + so_tbh + (uint64_t)((ks * 32) >> 4), ID2A, ks > 0, go);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tU, tWO + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero, go);
     PROF_STAMP(4, 27);
     mma_commit_pred(x.bar(B_V_EMPTY + s), go);            // the v tile may be refilled once MMA2 has read it
-    x.wait(B_M_FULL + s, par, E_MMA, 0);
-    tc_fence_after();
-    mma_ts4_block(tWO + 32, tU, (uint32_t)d_m + so, (uint32_t)(d_m >> 32), ID3B, go, 1u);   // O += U M^T: before the decay wait
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)                        // O += U M^T does not touch the state: issued before the wait
+      mma_ts_tf32_pred(tWO + 32, tU + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
     mma_commit_pred(x.bar(B_O_FULL + s), go);
     x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0); // decay St <- St diag(2^G31) finished
     tc_fence_after();
-    mma3s_block(tS, tU, (uint32_t)d_kr + so, (uint32_t)(d_kr >> 32), ID3A, go, 1u);
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tS, tU + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
     PROF_STAMP(4, 28);
     mma_commit_pred(x.bar(B_CONS_EMPTY + s), go);
     PROF_STAMP(4, 29);
@@ -931,16 +866,15 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
       mbar_init(x.bar(B_G_FULL + i), 1);
       mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
       mbar_init(x.bar(B_QK_FULL + i), 1);
-      mbar_init(x.bar(B_QK_EMPTY + i), 1);
+      mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
       mbar_init(x.bar(B_V_FULL + i), 1);
-      mbar_init(x.bar(B_V_EMPTY + i), 1);
       mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
       mbar_init(x.bar(B_CONS_EMPTY + i), 1);
-      mbar_init(x.bar(B_BF_FULL + i), PREP_WARPS);
       mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
-      mbar_init(x.bar(B_AM_FULL + i), 1);
       mbar_init(x.bar(B_INV_FULL + i), 1);
-      mbar_init(x.bar(B_M_FULL + i), 1);
+      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
+      mbar_init(x.bar(B_V_EMPTY + i), 1);
+      mbar_init(x.bar(B_L_EMPTY + i), 1);
       mbar_init(x.bar(B_O_FULL + i), 1);
       mbar_init(x.bar(B_O_EMPTY + i), 8);
     }
@@ -962,22 +896,21 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   if (warp == W_MMA) {
     role_mma(x, tmem, v_zero);
     __syncwarp();
-  } else if (warp == W_INV_A || warp == W_INV_B) {
-    role_inverse<FE>(p, x, tmem, warp == W_INV_A ? 0 : 1, lane);
+  } else if (warp == W_INV0 || warp == W_INV0 + 1) {
+    role_inverse(x, warp - W_INV0, lane);
   } else if (warp == W_LOAD) {
     role_loader<FE>(p, maps, x, lane);
     __syncwarp();
-  } else if (warp >= W_SCALE0 && warp < W_PREP_HI) {
+  } else if (warp < W_PREP0) {
     role_tmem<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
   } else {
-    // prep warps 2, 3, 6, 7 and 16..27, numbered 0..15; eight per group
-    const int pidx = warp >= W_PREP_HI ? warp - 12 : (warp & 1) + (warp >> 2) * 2;
-    role_prep<FE>(p, x, pidx / PREP_WARPS, (pidx % PREP_WARPS) * 32 + lane);
+    const int pt = tid - W_PREP0 * 32;
+    role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
   }
 
 #ifdef KDA_PROF
   if (lane == 0 && blockIdx.x == 0 && x.prof != nullptr) {
-    const int role = warp == W_MMA ? 4 : ((warp == W_INV_A || warp == W_INV_B) ? 3 : (warp == W_LOAD ? 1 : ((warp >= W_SCALE0 && warp < W_PREP_HI) ? 5 : 2)));
+    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_PREP0 ? 5 : 2)));
     atomicAdd(x.prof + role * 128 + 126, (unsigned long long)(clock64() - prof_t0));
     atomicAdd(x.prof + role * 128 + 127, 1ull);
   }

@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
   __shared__ unsigned long long keys[SORT_MAX];
   __shared__ unsigned char s_keep[SORT_MAX];     // checkpoint rows of sequence i: 0 = none / rejected, 1 = kept
   __shared__ int s_bits, s_overlap;
-  __shared__ int s_lp, s_cmax, s_uncut_work, s_work[N_CAND], s_pieces[N_CAND], s_longest[N_CAND];
+  __shared__ int s_lp, s_cmax, s_uncut_work, s_work[N_CAND], s_pieces[N_CAND], s_longest[N_CAND], s_ncut[N_CAND];
   __shared__ unsigned short s_off_a[CUT_MAX_SEQS], s_off_b[CUT_MAX_SEQS];
   __shared__ unsigned char s_cnt_a[CUT_MAX_SEQS], s_cnt_b[CUT_MAX_SEQS], s_off_m[CUT_MAX_SEQS], s_off_c[CUT_MAX_SEQS];
   const int tid = threadIdx.x, bd = blockDim.x, N = a.N;
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
   const int au = (a.ck_base != nullptr && a.ck_every > 0) ? a.ck_every / C : 1;    // alignment of a cut, in chunks
   if (tid == 0) s_lp = 0;
   if (a.max_pieces >= 2 && sorted && N <= CUT_MAX_SEQS && !noop) {
-    if (tid < N_CAND) { s_work[tid] = 0; s_pieces[tid] = 0; s_longest[tid] = 0; }
+    if (tid < N_CAND) { s_work[tid] = 0; s_pieces[tid] = 0; s_longest[tid] = 0; s_ncut[tid] = 0; }
     if (tid == 0) { s_uncut_work = 0; s_cmax = (int)((0x7fffffffULL - (keys[0] >> 32)) + C - 1) / C; }
     __syncthreads();
     const int cmax = s_cmax;
@@ -217,25 +217,31 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
           if (c > 0) atomicAdd(&s_work[k], c + TASK_OVERHEAD);
           atomicMax(&s_longest[k], c);
         } else {
-          const int p = (c + lp - 1) / lp;
-          atomicAdd(&s_work[k], (lp + TASK_OVERHEAD) * (3 * p - 4));      // 1 + 2 (p - 2) tasks, then p - 1 tasks
-          atomicAdd(&s_pieces[k], p);
-          atomicMax(&s_longest[k], lp);
+          atomicAdd(&s_pieces[k], (c + lp - 1) / lp);
+          atomicAdd(&s_ncut[k], 1);
         }
       }
     }
     __syncthreads();
     if (tid == 0) {
-      // times in 1/16 chunk steps; a launch cannot end before its longest task, nor before its share of the work
-      const long long H16 = 16LL * a.H;
-      long long best = max((long long)s_uncut_work * H16 / a.n_sm, 16LL * (cmax + TASK_OVERHEAD));
+      // Times in chunk steps.  A launch cannot end before its longest task, nor before its share of the work, nor before
+      // the SM that gets the most piece-sized tasks has run them all (pieces are equal, so few of them come in waves).
+      // A cut sequence of p pieces puts 2 p - 3 piece-sized tasks into the first launch and p - 1 into the second; the
+      // uncut sequences are spread over both launches so that both carry about the same work.
+      const long long Hh = a.H, nsm = a.n_sm;
+      long long best = max(((long long)s_uncut_work * Hh + nsm - 1) / nsm, (long long)(cmax + TASK_OVERHEAD));
       int best_lp = 0;
       for (int k = 0; k < N_CAND; k++) {
         const int lp = lp_of[k];
-        if (lp == 0 || s_pieces[k] == 0 || s_pieces[k] > a.max_pieces) continue;
-        const long long floor2 = 16LL * (max(s_longest[k], lp) + TASK_OVERHEAD + lp + TASK_OVERHEAD);
-        const long long t = max((long long)s_work[k] * H16 / a.n_sm, floor2) + 16LL * (SCAN_STEPS_X16 * (cand_pieces(k) - 2)) / 16 +
-                            16LL * LAUNCH_STEPS;
+        if (lp == 0 || s_ncut[k] == 0 || s_pieces[k] > a.max_pieces) continue;
+        const long long pt = lp + TASK_OVERHEAD;
+        const long long ka = 2LL * s_pieces[k] - 3LL * s_ncut[k], kb = (long long)s_pieces[k] - s_ncut[k];
+        const long long U = s_work[k];
+        const long long to_b = max(0LL, min(U, (pt * (ka + kb) + U) / 2 - pt * kb));
+        const long long wa = pt * ka + U - to_b, wb = pt * kb + to_b;
+        const long long ta = max(max((wa * Hh + nsm - 1) / nsm, ((ka * Hh + nsm - 1) / nsm) * pt), (long long)max(s_longest[k], lp) + TASK_OVERHEAD);
+        const long long tb = max(max((wb * Hh + nsm - 1) / nsm, ((kb * Hh + nsm - 1) / nsm) * pt), pt);
+        const long long t = ta + tb + (SCAN_STEPS_X16 * (long long)(cand_pieces(k) - 2) + 15) / 16 + LAUNCH_STEPS;
         if (t * 10 < best * 9) { best = t; best_lp = lp; }          // cut only for a clear gain
       }
       s_lp = best_lp;
@@ -294,7 +300,8 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
         const int c = (int)((0x7fffffffULL - (keys[j] >> 32)) + C - 1) / C;
         unsigned char ca = 0, cb = 0;
         if (c <= lp + lp / 4) {
-          const bool to_b = wpre < s_half && c > 0;
+          // (at most max_pieces uncut sequences move: the second launch's grid is sized for 2 * max_pieces tasks)
+          const bool to_b = wpre < s_half && c > 0 && tid * per + q < a.max_pieces;
           wpre += c > 0 ? c + TASK_OVERHEAD : 0;
           if (to_b) cb = 1; else ca = 1;
         } else {

@@ -35,7 +35,7 @@ struct PlanParams {
   int max_pieces;           // capacity: pieces of all cut sequences together (0 = never cut)
   int n_sm;                 // SMs of the device (cost model)
   int key_first;            // state layout of the launch (the transition maps are stored value-first either way)
-  Task* tasks_b;            // second launch: [N + max_pieces]
+  Task* tasks_b;            // second launch: [2 * max_pieces] (pieces, and up to max_pieces uncut sequences for balance)
   int* n_tasks_b;
   float* map_P;             // [max_pieces][H][128][128] transition maps
   float* map_L;             // [max_pieces][H][128][128] offsets; slot 0 of a cut sequence holds piece 0's end state

@@ -204,128 +204,6 @@ __device__ __forceinline__ void mma_commit_pred(uint32_t bar, uint32_t go) {
                " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" :: "r"(bar), "r"(go) : "memory");
 }
 
-// ---------------------------------------------------------------------------------------------- MMA groups
-// A group of consecutive MMAs of one product as ONE block of PTX: the issue predicate is formed once, the accumulate
-// flags are constants, and each step only adds a literal to the low word of a descriptor (the start-address field is
-// the low 14 bits; no carry can leave it for addresses inside shared memory) and to a tensor-memory column.  The
-// issuing warp shares its scheduler with six others, so every instruction saved per MMA shortens the per-chunk chain.
-// Descriptors are passed as (low word, high word).
-// MMA1: 16 tf32 steps of K = 8; A = 8 state columns per step, B = [kd ; qd] (K-major, 32-channel blocks 8192 bytes apart)
-__device__ __forceinline__ void mma1_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
-  asm volatile(
-      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
-      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
-      " setp.ne.b32 p0, %5, %5;\n"
-      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
-      " add.u32 lo, %2, 2;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 4;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 6;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 512;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 32;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 514;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 40;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 516;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 48;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 518;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 56;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1024;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 64;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1026;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 72;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1028;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 80;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1030;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 88;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1536;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 96;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1538;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 104;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1540;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 112;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 1542;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 120;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      "}\n"
-      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
-}
-
-// four tf32 steps of K = 8 over a K-major B tile of one 128-byte row block (Tb, M); the first step overwrites unless acc_first
-__device__ __forceinline__ void mma_ts4_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go, uint32_t acc_first) {
-  asm volatile(
-      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
-      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
-      " setp.ne.b32 p0, %6, 0;\n"
-      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
-      " add.u32 lo, %2, 2;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 4;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 6;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      "}\n"
-      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go), "r"(acc_first) : "memory");
-}
-
-// MMA3 state part: four tf32 steps of K = 8 over the MN-major kr tile (4096 bytes per step)
-__device__ __forceinline__ void mma3s_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go, uint32_t acc_first) {
-  asm volatile(
-      "{\n .reg .pred q, pt, p0;\n .reg .b32 lo, at;\n .reg .b64 d;\n"
-      " setp.ne.b32 q, %5, 0;\n setp.eq.b32 pt, %5, %5;\n"
-      " setp.ne.b32 p0, %6, 0;\n"
-      " add.u32 lo, %2, 0;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 0;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, p0;\n"
-      " add.u32 lo, %2, 256;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 8;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 512;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 16;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      " add.u32 lo, %2, 768;\n mov.b64 d, {lo, %3};\n add.u32 at, %1, 24;\n"
-      " @q tcgen05.mma.cta_group::1.kind::tf32 [%0], [at], d, %4, pt;\n"
-      "}\n"
-      :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go), "r"(acc_first) : "memory");
-}
-
-// MMA2 first part: two bf16 steps of K = 16, A = v tile (MN-major, 2048 bytes per step), B = bf16 Tb (64-byte rows)
-__device__ __forceinline__ void mma2a_block(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
-  asm volatile(
-      "{\n .reg .pred q, pt, p0;\n .reg .b32 la, lb;\n .reg .b64 da, db;\n"
-      " setp.ne.b32 q, %6, 0;\n setp.eq.b32 pt, %6, %6;\n setp.ne.b32 p0, %6, %6;\n"
-      " add.u32 la, %1, 0;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 0;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p0;\n"
-      " add.u32 la, %1, 128;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 2;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      "}\n"
-      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
-}
-
-// MMA0: eight bf16 steps of K = 16, A = interleaved q / k tiles (64-channel halves 8192 bytes apart), B = ki' (halves 4096 apart)
-__device__ __forceinline__ void mma0_block(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t go) {
-  asm volatile(
-      "{\n .reg .pred q, pt, p0;\n .reg .b32 la, lb;\n .reg .b64 da, db;\n"
-      " setp.ne.b32 q, %6, 0;\n setp.eq.b32 pt, %6, %6;\n setp.ne.b32 p0, %6, %6;\n"
-      " add.u32 la, %1, 0;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 0;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p0;\n"
-      " add.u32 la, %1, 2;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 2;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 4;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 4;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 6;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 6;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 512;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 256;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 514;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 258;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 516;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 260;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      " add.u32 la, %1, 518;\n mov.b64 da, {la, %2};\n add.u32 lb, %3, 262;\n mov.b64 db, {lb, %4};\n"
-      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n"
-      "}\n"
-      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(go) : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------- tile addressing
 // K-major SW128 tile of 32-bit elements, rows of 128 bytes (32 elements), K blocks `kblock_bytes` apart:
 // byte offset of element (row, k).
