@@ -276,12 +276,41 @@ def run_layouts(args, dev, kda_b200):
         if kda_b200.status_bits(launch) != 0 or kda_b200.kernel_error(launch) != 0:
             raise SystemExit(f"bench: layout {name} reported a table or kernel error")
         res[name] = {"ms": round(ms, 4), "tokens_per_s": T / (ms * 1e-3)}
+    # ---- host latency of the public calls (no synchronisation inside; the reference states limits for its run():
+    # <= 1 ms + 0.01 ms per sequence for a repeated layout, <= 2 ms + 0.025 ms per sequence for a new one,
+    # kda/b200/README.md:39-41).  Nothing is planned on the host here, so "new" and "repeated" layouts cost the same.
+    host = {}
+    for n_seq in (1, 32, 512):
+        lens_h = [T // n_seq] * n_seq
+        cu_h = torch.tensor([0, *torch.tensor(lens_h).cumsum(0).tolist()], dtype=torch.int64, device=dev)
+        slots_h = slots[:n_seq].contiguous()
+
+        def t_of(fn, reps=15):
+            ts = []
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                r = fn()
+                ts.append((time.perf_counter() - t0) * 1e6)
+                del r
+            return sorted(ts)[len(ts) // 2]
+
+        mk = lambda: kda_b200.prepare_plain(q, k, v, g, beta, D ** -0.5, pool, False, cu_h, dynamic_layout=True,  # noqa: E731
+                                            ssm_state_indices=slots_h)
+        lh = mk()
+        host[f"N={n_seq}"] = {"prepare_us": round(t_of(mk), 1), "launch_us": round(t_of(lh), 1),
+                              "run_us": round(t_of(lambda: mk()()), 1)}
+        limit_us = 1000.0 + 10.0 * n_seq
+        if host[f"N={n_seq}"]["run_us"] > limit_us:
+            raise SystemExit(f"bench: host time of run() with {n_seq} sequences is {host[f'N={n_seq}']['run_us']} us, "
+                             f"over the reference's limit of {limit_us} us")
     print(json.dumps({"metric": "KDA prefill tokens/s (H=64,K=V=128, one CUDA graph over batch layouts)", "unit": "tokens/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16",
                       "data": "synthetic",
                       "config": {"workload": "configs[4]: token capacity 32768, H=64, 512 sequence slots, pool of 1024 slots, "
                                              "g=logsigmoid(N(2,1)); one captured graph, cu_seqlens rewritten in place"},
-                      "layouts": res}))
+                      "layouts": res, "host_latency": host,
+                      "host_latency_limit": "run() <= 1000 us + 10 us per sequence (kda/b200/README.md:39-41); asserted"}))
     return 0
 
 

@@ -229,7 +229,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
     if (rc != KDA_OK) return rc;
   }
   // first launch: every uncut sequence (or all of them), piece 0 and the map chains of the cut ones
-  e = umma ? kda::launch_chunk_umma(p, maps, a->N + 2 * pieces, stream) : kda::launch_chunk_fwd(p, a->N + 2 * pieces, stream);
+  e = umma ? kda::launch_chunk_umma(p, maps, a->N + 2 * pieces, stream, true) : kda::launch_chunk_fwd(p, a->N + 2 * pieces, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   if (pieces > 0) {
     // entering states of the later pieces, then those pieces (both launches find nothing to do when nothing was cut)
@@ -321,7 +321,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
     kda::TmaMaps maps;
     rc = fill_tma_maps(maps, a);
     if (rc != KDA_OK) return rc;
-    e = kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream);
+    e = kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream, true);
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;

@@ -816,6 +816,9 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   const int H = p.H;
   const int rank = blockIdx.x / H, h = blockIdx.x % H;
 
+  // Launched as a programmatic dependent of the planner (its CTAs become resident while the planner still runs): wait
+  // here until the planner's writes (status, task table) are visible.  A no-op for an ordinary launch.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   if (p.status[0] & 1) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
     const long long rows = p.T * H;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x)
@@ -926,7 +929,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
 
 }  // namespace u
 
-cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream) {
+cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner) {
   // one instantiation per (front-end, state layout): smaller code per launch, and instruction-cache footprint is what
   // bounds this role-specialised kernel
   typedef void (*Kern)(const ChunkParams, const TmaMaps);
@@ -944,8 +947,19 @@ cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_t
   }
   const long long blocks = (long long)n_task_cap * p.H;
   if (blocks <= 0) return cudaSuccess;
-  kerns[p.frontend ? 1 : 0][p.key_first ? 1 : 0]<<<(unsigned)blocks, u::THREADS, u::SMEM_BYTES, stream>>>(p, maps);
-  return cudaGetLastError();
+  // Chained behind the planner by programmatic dependent launch when it directly follows it in the stream (function
+  // of kda/b200/csrc/w3/base/cake/launch_m128.cu:37-60): the launch latency hides under the planner.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(u::THREADS);
+  cfg.dynamicSmemBytes = u::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = after_planner ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kerns[p.frontend ? 1 : 0][p.key_first ? 1 : 0], p, maps);
 }
 
 }  // namespace kda

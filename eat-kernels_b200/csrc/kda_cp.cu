@@ -11,6 +11,7 @@ namespace kda {
 
 // ------------------------------------------------------------------------------------------------ segment tasks
 __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // see kda_plan_kernel
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n_seg; i += gridDim.x * blockDim.x) {
     long long t0 = a.t0[i], t1 = a.t1[i];
     if (t0 < 0) t0 = 0;

@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
   __shared__ unsigned short s_off_a[CUT_MAX_SEQS], s_off_b[CUT_MAX_SEQS];
   __shared__ unsigned char s_cnt_a[CUT_MAX_SEQS], s_cnt_b[CUT_MAX_SEQS], s_off_m[CUT_MAX_SEQS], s_off_c[CUT_MAX_SEQS];
   const int tid = threadIdx.x, bd = blockDim.x, N = a.N;
+  // the chunk kernel chained behind this launch may become resident now (it waits for this kernel's results itself)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (tid == 0) { s_bits = 0; s_overlap = 0; }
   __syncthreads();
   // rows [v, v + cnt) of sequence i and whether they lie inside the checkpoint buffer

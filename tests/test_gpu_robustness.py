@@ -110,3 +110,29 @@ def test_beta_is_read_in_place_for_any_head_count(kda):
         a = (a[0].clone(), a[1].clone())
         b = kda.run(*[t.contiguous() if torch.is_tensor(t) else t for t in view])
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_host_latency_of_run_is_within_the_reference_limits(kda):
+    """The reference states host-side limits for run(): <= 1 ms + 0.01 ms per sequence for a repeated layout and
+    <= 2 ms + 0.025 ms per sequence for a new one (kda/b200/README.md:39-41).  Nothing is planned on the host here (the
+    schedule is made on the device at every launch), so every layout counts as new and must meet the tighter limit."""
+    import time
+    H, T = 8, 4096
+    inputs = ko.make_inputs_raw(H, [T], 41)
+    q, k, v, g, beta, A_log, dt_bias, scale = to_dev(inputs[:8])
+    for n_seq in (1, 32, 512):
+        lens = [T // n_seq] * n_seq
+        pool = torch.zeros(n_seq, H, D, D, device=DEV)
+        idx = torch.arange(n_seq, dtype=torch.int32, device=DEV)
+        cu = cu_of(lens)
+        call = lambda: kda.run(q, k, v, g, beta, A_log, dt_bias, scale, pool, cu, ssm_state_indices=idx)  # noqa: E731
+        call()
+        times = []
+        for _ in range(9):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            call()
+            times.append(time.perf_counter() - t0)
+        torch.cuda.synchronize()
+        med_ms = sorted(times)[len(times) // 2] * 1e3
+        assert med_ms <= 1.0 + 0.01 * n_seq, f"run() with {n_seq} sequences took {med_ms:.3f} ms on the host"
