@@ -382,7 +382,7 @@ int kda_prefill_plan_counts(const KdaPrefillArgs* a, int32_t* counts, void* stre
 }
 
 int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters) {
-  if (wait_limit_us < 0 || (flags & ~kda::DBG_SKIP_V_STREAM)) return KDA_ERR_ARG;
+  if (wait_limit_us < 0 || (flags & ~kda::DBG_STALL_V_STREAM)) return KDA_ERR_ARG;
   g_wait_limit_ns = (unsigned long long)wait_limit_us * 1000ull;
   g_debug_flags = flags;
   g_prof = reinterpret_cast<unsigned long long*>(prof_counters);

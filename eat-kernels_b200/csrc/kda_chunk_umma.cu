@@ -123,6 +123,27 @@ struct Ctx {
 // One elected lane drives the copy engine: per chunk it arms the stage's mbarrier with the byte count and issues the
 // tile copies (g, q, k into the raw stage, v straight into the MMA2 operand slot of the consumer stage, whose
 // MN-major 128-byte-swizzled layout is exactly what the engine writes).
+// Rare paths of the loader, out of line: its polling loop sits on the refill latency of every tile, and anything that
+// adds live state or code to it costs measurable time per chunk.
+__device__ __noinline__ bool loader_idle_expired(unsigned long long idle_ns, volatile int* abort_flag) {
+  if (idle_ns <= wait_limit_of(abort_flag)) return false;
+  atomicCAS(const_cast<int*>(abort_flag), 0, E_LOAD);
+  return true;
+}
+// Before the CTA may leave, every copy the loader issued has landed (on the normal path the consumers saw to that
+// long ago and these waits return at once; after a give-up they keep the copy engine from writing into a dead CTA).
+// A stage's full barrier is not re-armed after its last copy, so the parity of that last phase is still testable.
+__device__ __noinline__ void loader_drain(uint32_t bars, volatile int* abort_flag, int cg, int cq, int cv) {
+#pragma unroll 1
+  for (int st = 0; st < 3; st++) {
+    const int issued = st == 0 ? cg : (st == 1 ? cq : cv);
+    const int fb = st == 0 ? B_G_FULL : (st == 1 ? B_QK_FULL : B_V_FULL);
+    for (int c = max(0, issued - 2); c < issued; c++)
+      if (!mbar_wait_drain(bars + 8u * (uint32_t)(fb + (c & 1)), (uint32_t)((c >> 1) & 1), abort_flag))
+        atomicCAS(const_cast<int*>(abort_flag), 0, E_DRAIN + fb);
+  }
+}
+
 template <int FE>
 __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x, int lane) {
   // Three independent copy streams (g; q and k; v), each with its own full / empty barrier pair per stage: the gate
@@ -133,8 +154,6 @@ __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x
   if (lane != 0) return;
   const int n = x.nchunks;
   int cg = 0, cq = 0, cv = 0;                 // next chunk of each stream
-  const bool skip_v = (p.debug_flags & DBG_SKIP_V_STREAM) != 0;   // diagnostic: the v stream is never issued
-  if (skip_v) cv = n;
   unsigned idle = 0;
   unsigned long long t_idle = 0;
 #pragma unroll 1
@@ -188,26 +207,11 @@ __device__ void role_loader(const ChunkParams& p, const TmaMaps& m, const Ctx& x
       if ((++idle & 1023u) == 0) {
         const unsigned long long now = global_timer_ns();
         if (t_idle == 0) t_idle = now;
-        else if (now - t_idle > wait_limit_of(x.abort_flag)) {
-          atomicCAS(const_cast<int*>(x.abort_flag), 0, E_LOAD);
-          break;
-        }
+        else if (loader_idle_expired(now - t_idle, x.abort_flag)) break;
       }
     }
   }
-  // Before the CTA may leave, every copy this lane issued has landed (on the normal path the consumers saw to that
-  // long ago and these waits return at once; after a give-up they keep the copy engine from writing into a dead CTA).
-  // A stage's full barrier is not re-armed after its last copy, so the parity of that last phase is still testable.
-  if (skip_v) cv = 0;
-#pragma unroll
-  for (int st = 0; st < 3; st++) {
-    const int issued = st == 0 ? cg : (st == 1 ? cq : cv);
-    const int fb = st == 0 ? B_G_FULL : (st == 1 ? B_QK_FULL : B_V_FULL);
-#pragma unroll 1
-    for (int c = max(0, issued - 2); c < issued; c++)
-      if (!mbar_wait_drain(x.bar(fb + (c & 1)), (uint32_t)((c >> 1) & 1), x.abort_flag))
-        atomicCAS(const_cast<int*>(x.abort_flag), 0, E_DRAIN + fb);
-  }
+  loader_drain(x.bars, x.abort_flag, cg, cq, (p.debug_flags & DBG_STALL_V_STREAM) ? 0 : cv);
 }
 
 template <int FE>
@@ -272,10 +276,6 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         if (16 * half + i >= nvalid) a[i] = 0.0f;
         if (i > 0) a[i] += a[i - 1];
       }
-      // Range of the primed operands: their exponents are taken relative to the decay after token 15, so the largest
-      // ones belong to token 0 (first half) and token 31 (second half).  Beyond 2^126 they are clamped below and the
-      // intra-chunk products of this chunk are no longer exact: report it.
-      if (half == 0 ? (a[0] - a[15] > 126.0f) : (a[15] < -126.0f)) *range_flag = 1;
       if (half == 0) tot[ch] = a[15];
       PROF_STAMP(2, 10);
       named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
@@ -287,6 +287,12 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
       }
       if (half == 1) {
         const float r = tot[ch];
+        // Range of the primed operands: their exponents are taken relative to the decay after token 15, so the largest
+        // ones belong to token 0 (at most -r) and token 31 (a[15], still the second half's own sum here).  Beyond
+        // 2^126 they are clamped below and the intra-chunk products of this chunk are no longer exact: report it.
+        // (Checked here, by the threads that hold both numbers anyway, and reported by one lane per warp: these warps
+        // set the pace of the kernel, and a separate test in the first half of step A cost 2.7 % of it.)
+        if (__any_sync(0xffffffffu, fminf(r, a[15]) < -126.0f) && lane == 0) *range_flag = 1;
 #pragma unroll
         for (int i = 0; i < 16; i++) a[i] += r;
         fr[ch] = r;
@@ -870,7 +876,8 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
       mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
       mbar_init(x.bar(B_QK_FULL + i), 1);
       mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
-      mbar_init(x.bar(B_V_FULL + i), 1);
+      // diagnostic switch: the v barriers expect one arrival more than they will ever get, so their waiters give up
+      mbar_init(x.bar(B_V_FULL + i), (p.debug_flags & DBG_STALL_V_STREAM) ? 2 : 1);
       mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
       mbar_init(x.bar(B_CONS_EMPTY + i), 1);
       mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);

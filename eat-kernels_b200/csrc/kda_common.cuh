@@ -60,7 +60,7 @@ struct ChunkParams {
 };
 
 // Diagnostic switches of the tcgen05 kernel (set only through kda_debug_configure).
-constexpr int DBG_SKIP_V_STREAM = 1;   // the loader never issues the v copies: a waiter runs into its bound
+constexpr int DBG_STALL_V_STREAM = 1;  // the v tiles never count as arrived: their waiters run into the bound
 
 // ----------------------------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -213,8 +213,8 @@ const char* kda_version(void);
  *   wait_limit_us  bound of every wait inside the tcgen05 kernel (0 = the built-in two seconds).  When a wait runs out
  *                  the kernel finishes its control flow, waits for its own copies and tensor-core work, frees tensor
  *                  memory and writes a code to status[2].
- *   flags          bit 0: the kernel's loader never issues the v copies, so that a waiter runs into the bound
- *                  (used to test the give-up path without faulting or hanging anything); 0 = normal operation.
+ *   flags          bit 0: the arrival of the v tiles is never signalled to their consumers, so that a waiter runs into
+ *                  the bound (used to test the give-up path without faulting or hanging anything); 0 = normal.
  *   prof_counters  device uint64[1024] receiving per-role cycle counters in builds compiled with -DKDA_PROF; NULL else. */
 int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters);
 

@@ -23,10 +23,10 @@ def kda():
 
 
 def test_bounded_wait_gives_up_and_the_next_launch_is_correct(kda):
-    """The kernel's hand-offs are bounded waits.  With the diagnostic switch that keeps the loader from ever issuing the
-    v copies, the first waiter on a v tile runs into the (shortened) bound: the kernel must still end by itself, free
-    its tensor memory, report a nonzero code in status[2] and leave the device usable.  Nothing faults or hangs: the
-    flag that would end the wait is simply never set."""
+    """The kernel's hand-offs are bounded waits.  With the diagnostic switch under which the arrival of the v tiles is
+    never signalled, the first waiter on a v tile runs into the (shortened) bound: the kernel must still end by itself,
+    free its tensor memory, report a nonzero code in status[2] and leave the device usable.  Nothing faults or hangs:
+    the flag that would end the wait is simply never set."""
     from kda_b200 import _cabi
     lib = _cabi.lib()
     lens = [300, 64, 1000]
@@ -34,7 +34,7 @@ def test_bounded_wait_gives_up_and_the_next_launch_is_correct(kda):
     gold_o, gold_s, _ = gold_raw(inputs, lens)
     d = to_dev(inputs)
     launch = kda.prepare(*d)
-    assert lib.kda_debug_configure(200, 1, None) == 0          # 200 us bound, v stream never issued
+    assert lib.kda_debug_configure(200, 1, None) == 0          # 200 us bound, v tiles never signalled
     try:
         launch()
         torch.cuda.synchronize()                               # returns: every CTA gave up and left
