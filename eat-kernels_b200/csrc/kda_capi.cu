@@ -77,7 +77,7 @@ int sm_count() {
 int check_tokens(const KdaPrefillArgs* a) {
   if (a == nullptr) return KDA_ERR_ARG;
   if (a->H <= 0 || a->N < 0 || a->T < 0) return KDA_ERR_ARG;
-  if (a->kernel != KDA_KERNEL_TCGEN05 && a->kernel != KDA_KERNEL_MMA_SYNC) return KDA_ERR_ARG;
+  if (a->kernel != KDA_KERNEL_TCGEN05 && a->kernel != KDA_KERNEL_MMA_SYNC && a->kernel != KDA_KERNEL_TCGEN05_DUAL) return KDA_ERR_ARG;
   if (a->frontend != KDA_FRONTEND_RAW && a->frontend != KDA_FRONTEND_PLAIN) return KDA_ERR_ARG;
   if (a->state_layout != KDA_STATE_VALUE_FIRST && a->state_layout != KDA_STATE_KEY_FIRST) return KDA_ERR_ARG;
   if (a->T > 0) {
@@ -305,6 +305,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   sp.need_map = s->seg_need_map;
   sp.src_base = a->src_base; sp.src_stride = a->src_slot_stride;
   sp.no_out = maps_only ? 1 : 0;
+  sp.dual = a->kernel == KDA_KERNEL_TCGEN05_DUAL;  // a mapped segment as one dual-chain task instead of two tasks
   sp.P = s->P; sp.S_loc = s->S_loc;
   sp.tasks = w.tasks; sp.n_tasks = w.n_tasks; sp.status = a->status;
   cudaError_t e = kda::launch_seg_plan(sp, stream);
@@ -321,7 +322,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
     kda::TmaMaps maps;
     rc = fill_tma_maps(maps, a);
     if (rc != KDA_OK) return rc;
-    e = kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream, true);
+    e = sp.dual ? kda::launch_chunk_dual(p, maps, s->n_seg, stream, true) : kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream, true);
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;

@@ -60,7 +60,7 @@ constexpr int OFF_FR = OFF_DEC + 2048;                        // per prep group:
 constexpr int OFF_BETA = OFF_FR + 2 * 1536;                   // raw-stage beta: 2 x 128
 constexpr int OFF_LBETA = OFF_BETA + 256;                     // beta next to L: 2 x 128
 constexpr int OFF_BAR = OFF_LBETA + 256;                      // mbarriers
-constexpr int NUM_BARS = 32;
+constexpr int NUM_BARS = 34;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // +0 tmem slot, +8 abort code, +12 range flag, +16 wait limit (ns)
 constexpr int SMEM_BYTES = OFF_MISC + 64;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -68,7 +68,8 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 // mbarrier indices
 constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
               B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20, B_V_EMPTY = 21,
-              B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29;
+              B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29,
+              B_MMA1_DONE_T = 31, B_S_READY_T = 32;   // second chain of the dual-chain kernel
 
 // tensor-memory columns
 constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
@@ -934,6 +935,336 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
 }
 
+// ================================================================================================ dual-chain kernel
+// Context parallelism needs, for a token segment whose entering state is not known yet, TWO chains over the same tokens:
+// chain L from S = 0 with the real v (o_loc, S_loc) and chain Tr from S = I with v = 0 (Qt, P).  Everything the
+// preparation warps, the loader and the inverse warps produce is the same for both, and the tensor pipe is busy a
+// quarter of the time, so one task runs both chains over ONE operand preparation: a second state in tensor-memory
+// columns 128-255, each MMA group issued twice, the tensor-memory warps serving both states (function of the reference's
+// dual kernel, kda/b200/csrc/w3/base/cake_dual/kda_m128.cu:821-823, kda/b200/csrc/w3/base/dual.py:1-4).
+// A kernel of its own (the single-chain kernel above is untouched): tasks with TF_DUAL run both chains, the others one.
+// Tensor memory of a dual task: S_L 0-127, S_T 128-255, [W | O] of L 256-319, of T 320-383 (one buffer per chain: the
+// other chain's work hides the read-out), U of L 384-447, of T 448-511 (two stages each).  A single-chain task in this
+// kernel keeps the single-chain kernel's map for [W | O] (columns 128-255, one buffer per stage): with one buffer the
+// read-out of O would sit on its serial chain (measured: 37 % slower).
+constexpr uint32_t TD_S0 = 0, TD_S1 = 128, TD_WO0 = 256, TD_WO1 = 320, TD_U0 = 384, TD_U1 = 448;
+
+__device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any, bool dual_any) {
+  const uint32_t go = elect_one();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_any, 0);
+  const bool v_zero = __shfl_sync(0xffffffffu, (int)v_zero_any, 0) != 0;
+  const bool dual = __shfl_sync(0xffffffffu, (int)dual_any, 0) != 0;
+  const int nchunks = __shfl_sync(0xffffffffu, x.nchunks, 0);
+  const uint32_t sb = smem_u32(x.smem);
+  constexpr uint32_t ID1 = make_idesc(FMT_TF32, 128, 64, 0, 0, 0);
+  constexpr uint32_t ID2A = make_idesc(FMT_BF16, 128, 32, 1, 0, 0);
+  constexpr uint32_t ID2B = make_idesc(FMT_TF32, 128, 32, 0, 0, 1);
+  constexpr uint32_t ID3A = make_idesc(FMT_TF32, 128, 128, 0, 1, 0);
+  constexpr uint32_t ID3B = make_idesc(FMT_TF32, 128, 32, 0, 0, 0);
+  const uint64_t d_kdqd = make_sdesc(sb + OFF_CONS + CS_KDQD, 16, 1024, LAYOUT_SW128);
+  const uint64_t d_v = make_sdesc(sb + OFF_CONS + CS_V, 4096, 1024, LAYOUT_SW128);
+  const uint64_t d_tbh = make_sdesc(sb + OFF_TBH, 16, 512, LAYOUT_SW64);
+  const uint64_t d_tb = make_sdesc(sb + OFF_CONS + CS_TB, 16, 1024, LAYOUT_SW128);
+  const uint64_t d_kr = make_sdesc(sb + OFF_CONS + CS_KR, 512, 2048, LAYOUT_SW128_BASE32B);
+  const uint64_t d_m = make_sdesc(sb + OFF_CONS + CS_M, 16, 1024, LAYOUT_SW128);
+  const uint32_t tS0 = tmem + TD_S0, tS1 = tmem + TD_S1, tWO1 = tmem + TD_WO1;
+  x.wait(B_S_READY, 0, E_MMA, 0);                  // initial states are in tensor memory
+  if (dual) x.wait(B_S_READY_T, 0, E_MMA, 0);
+#pragma unroll 1
+  for (int c = 0; c < nchunks; c++) {
+    const int s = c & 1;
+    const uint32_t par = (uint32_t)((c >> 1) & 1), cpar = (uint32_t)(c & 1);
+    const uint64_t so = (uint64_t)(s * (CS_STAGE >> 4));
+    const uint64_t so_tbh = (uint64_t)(s * (2048 >> 4));
+    const uint32_t tU0 = tmem + TD_U0 + 32 * s, tU1 = tmem + TD_U1 + 32 * s;
+    // chain L's [W | O]: per chain (one phase per chunk) in a dual task, per stage as in the single-chain kernel else
+    const uint32_t tWO0 = dual ? tmem + TD_WO0 : tmem + TM_WO + 64 * s;
+    const int ob0 = dual ? 0 : s;
+    x.wait(B_P1_FULL + s, par, E_MMA, 0);
+    x.wait(B_O_EMPTY + ob0, (dual ? cpar : par) ^ 1, E_MMA, 0);
+    tc_fence_after();
+#pragma unroll
+    for (int ks = 0; ks < 16; ks++)
+      mma_ts_tf32_pred(tWO0, tS0 + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
+    mma_commit_pred(x.bar(B_MMA1_DONE), go);
+    if (dual) {
+      x.wait(B_O_EMPTY + 1, cpar ^ 1, E_MMA, 0);
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 16; ks++)
+        mma_ts_tf32_pred(tWO1, tS1 + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
+      mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
+    }
+    mma_commit_pred(x.bar(B_KDQD_EMPTY + s), go);
+    x.wait(B_INV_FULL + s, par, E_MMA, 0);
+    x.wait(B_V_FULL + s, par, E_MMA, 0);
+    tc_fence_after();
+    if (!v_zero) {
+#pragma unroll
+      for (int ks = 0; ks < 2; ks++)
+        mma_ss_f16_pred(tU0, d_v + so + (uint64_t)((2 * ks * 1024) >> 4), d_tbh + so_tbh + (uint64_t)((ks * 32) >> 4), ID2A, ks > 0, go);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tU0, tWO0 + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero, go);
+    if (dual) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++)                      // the transition chain has v = 0: U = - W Tb^T
+        mma_ts_tf32_pred(tU1, tWO1 + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, ks > 0, go);
+    }
+    mma_commit_pred(x.bar(B_V_EMPTY + s), go);
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tWO0 + 32, tU0 + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
+    mma_commit_pred(x.bar(B_O_FULL + ob0), go);
+    if (dual) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++)
+        mma_ts_tf32_pred(tWO1 + 32, tU1 + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
+      mma_commit_pred(x.bar(B_O_FULL + 1), go);
+    }
+    x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0);
+    tc_fence_after();
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tS0, tU0 + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
+    if (dual) {
+      x.wait(B_S_READY_T, (uint32_t)((c + 1) & 1), E_MMA, 0);
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++)
+        mma_ts_tf32_pred(tS1, tU1 + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
+    }
+    mma_commit_pred(x.bar(B_CONS_EMPTY + s), go);
+  }
+  mma_commit_pred(x.bar(B_MMA1_DONE), go);         // the final states are complete
+  if (dual) mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
+  mma_commit_pred(x.bar(B_DRAIN), go);
+  if (!mbar_wait_drain(x.bar(B_DRAIN), 0, x.abort_flag)) atomicCAS(const_cast<int*>(x.abort_flag), 0, E_DRAIN + B_DRAIN);
+}
+
+// St <- St diag(d) for this warp's 64 state columns (four 16-column pieces, the load of one in flight while the
+// previous one is scaled and stored)
+__device__ __forceinline__ void decay64(uint32_t tS, const float* dcol) {
+  uint32_t a[16], b[16], e[16];
+  tmem_ld16(tS, a);
+  tmem_ld16(tS + 16, b);
+  tmem_wait_ld();
+  scale16(a, dcol);
+  tmem_st16(tS, a);
+  tmem_ld16(tS + 32, e);
+  scale16(b, dcol + 16);
+  tmem_st16(tS + 16, b);
+  tmem_ld16(tS + 48, a);
+  tmem_wait_ld();
+  scale16(e, dcol + 32);
+  tmem_st16(tS + 32, e);
+  scale16(a, dcol + 48);
+  tmem_st16(tS + 48, a);
+  tmem_wait_st();
+}
+
+template <int KF>
+__device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int hf, int lane, bool dual) {
+  const int v = 32 * quarter + lane;
+  const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+  const uint32_t tS0 = tmem + TD_S0 + lane_base + 64 * hf, tS1 = tmem + TD_S1 + lane_base + 64 * hf;
+  // ---- initial states -> tensor memory: chain L as the task says, chain Tr the identity
+#pragma unroll 1
+  for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+#pragma unroll 1
+    for (int j = 0; j < 2; j++) {
+      const int col0 = 64 * hf + 32 * j;
+      uint32_t r[32];
+      if (ch == 1 || (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY))) {
+        const float one = (ch == 1 || (task.flags & TF_INIT_IDENTITY)) ? 1.0f : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) r[i] = __float_as_uint((col0 + i == v) ? one : 0.0f);
+      } else {
+        const float* src = task.src + (size_t)x.h * STATE_ELEMS;
+        if (!KF) {
+          const float4* s4 = reinterpret_cast<const float4*>(src + v * D + col0);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float4 f = s4[i];
+            r[4 * i] = __float_as_uint(f.x); r[4 * i + 1] = __float_as_uint(f.y); r[4 * i + 2] = __float_as_uint(f.z); r[4 * i + 3] = __float_as_uint(f.w);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) r[i] = __float_as_uint(src[(col0 + i) * D + v]);
+        }
+      }
+      tmem_st32((ch ? tS1 : tS0) + 32 * j, r);
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(x.bar(ch ? B_S_READY_T : B_S_READY));
+  }
+
+  __nv_bfloat16* obase0 = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
+  __nv_bfloat16* obase1 = p.out_aux + (long long)x.h * D + v;
+#pragma unroll 1
+  for (int c = 0; c <= x.nchunks; c++) {
+    const bool last = c == x.nchunks;
+    const float* dcol = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 3) * D + 64 * hf;
+#pragma unroll 1
+    for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+      x.wait(ch ? B_MMA1_DONE_T : B_MMA1_DONE, (uint32_t)(c & 1), E_SCALE);
+      tc_fence_after();
+      const uint32_t tS = ch ? tS1 : tS0;
+      if (last) {
+        // final states: chain L in the launch's layout, the transition map always value-first
+        float* dst = ch ? task.dst2 : task.dst;
+        if (dst != nullptr) {
+          dst += (size_t)x.h * STATE_ELEMS;
+          if (ch == 1 || !KF || (task.flags & TF_DST_VF)) store_state_rows<0>(tS, dst, nullptr, 0, v, hf);
+          else store_state_rows<KF>(tS, dst, nullptr, 0, v, hf);
+        }
+      } else {
+        decay64(tS, dcol);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x.bar(ch ? B_S_READY_T : B_S_READY));
+      }
+    }
+    if (last) break;
+    // ---- output rows of this chunk, chain L then chain Tr
+    const int nvalid = min(C, x.len - c * C);
+#pragma unroll 1
+    for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+      const int ob = dual ? ch : (c & 1);                  // see role_mma_dual
+      x.wait(B_O_FULL + ob, (uint32_t)(dual ? (c & 1) : ((c >> 1) & 1)), E_EPI);
+      tc_fence_after();
+      uint32_t o[16];
+      tmem_ld16(tmem + (dual ? (ch ? TD_WO1 : TD_WO0) : TM_WO + 64 * (c & 1)) + 32 + 16 * hf + lane_base, o);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + ob));
+      if (!(task.flags & TF_NO_OUT)) {
+        __nv_bfloat16* orow = (ch ? obase1 : obase0) + (x.t0 + (long long)c * C + 16 * hf) * p.ldo;
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+          if (16 * hf + i < nvalid) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
+      }
+    }
+  }
+}
+
+template <int FE, int KF>
+__global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = tid >> 5;
+  const int H = p.H;
+  const int rank = blockIdx.x / H, h = blockIdx.x % H;
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");     // chained behind the task planner (see the kernel above)
+  if (rank >= *p.n_tasks) return;
+  const Task task = p.tasks[rank];
+  Ctx x;
+  x.smem = smem;
+  x.bars = smem_u32(smem + OFF_BAR);
+  x.abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
+  x.h = h;
+  x.len = task.len;
+  x.nchunks = (task.len + C - 1) / C;
+  x.t0 = task.t0;
+#ifdef KDA_PROF
+  x.prof = p.prof;
+  const long long prof_t0 = clock64();
+#endif
+  const bool dual = (task.flags & TF_DUAL) != 0;
+  if (x.nchunks == 0) {
+    // empty run: chain L passes its state through, the transition map of no tokens is the identity
+    for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+      float* dst = ch ? task.dst2 : task.dst;
+      if (dst == nullptr) continue;
+      dst += (size_t)h * STATE_ELEMS;
+      const bool ident = ch == 1 || (task.flags & TF_INIT_IDENTITY);
+      const float* src = (ch == 1 || (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY))) ? nullptr : task.src + (size_t)h * STATE_ELEMS;
+      if (src == dst) continue;
+      for (int i = tid; i < STATE_ELEMS / 4; i += THREADS) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src != nullptr) f = reinterpret_cast<const float4*>(src)[i];
+        else if (ident) {
+          const int row = (4 * i) / D, col = (4 * i) % D;
+          f = make_float4(row == col ? 1.f : 0.f, row == col + 1 ? 1.f : 0.f, row == col + 2 ? 1.f : 0.f, row == col + 3 ? 1.f : 0.f);
+        }
+        reinterpret_cast<float4*>(dst)[i] = f;
+      }
+    }
+    return;
+  }
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+  volatile int* range_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 12);
+  if (tid == 0) {
+    *x.abort_flag = 0;
+    *range_flag = 0;
+    *reinterpret_cast<volatile unsigned long long*>(smem + OFF_MISC + 16) = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
+    for (int i = 0; i < 2; i++) {
+      mbar_init(x.bar(B_G_FULL + i), 1);
+      mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_QK_FULL + i), 1);
+      mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
+      mbar_init(x.bar(B_V_FULL + i), 1);
+      mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
+      mbar_init(x.bar(B_CONS_EMPTY + i), 1);
+      mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
+      mbar_init(x.bar(B_INV_FULL + i), 1);
+      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
+      mbar_init(x.bar(B_V_EMPTY + i), 1);
+      mbar_init(x.bar(B_L_EMPTY + i), 1);
+      mbar_init(x.bar(B_O_FULL + i), 1);       // here: one per chain
+      mbar_init(x.bar(B_O_EMPTY + i), 8);
+    }
+    mbar_init(x.bar(B_MMA1_DONE), 1);
+    mbar_init(x.bar(B_S_READY), 8);
+    mbar_init(x.bar(B_MMA1_DONE_T), 1);
+    mbar_init(x.bar(B_S_READY_T), 8);
+    mbar_init(x.bar(B_DRAIN), 1);
+    fence_barrier_init();
+  }
+  if (warp == W_MMA) {
+    tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const bool v_zero = (task.flags & TF_V_ZERO) != 0;
+
+  if (warp == W_MMA) {
+    role_mma_dual(x, tmem, v_zero, dual);
+    __syncwarp();
+  } else if (warp == W_INV0 || warp == W_INV0 + 1) {
+    role_inverse(x, warp - W_INV0, lane);
+  } else if (warp == W_LOAD) {
+    role_loader<FE>(p, maps, x, lane);
+    __syncwarp();
+  } else if (warp < W_PREP0) {
+    role_tmem_dual<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane, dual);
+  } else {
+    const int pt = tid - W_PREP0 * 32;
+    role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
+  }
+#ifdef KDA_PROF
+  if (lane == 0 && blockIdx.x == 0 && x.prof != nullptr) {
+    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_PREP0 ? 5 : 2)));
+    atomicAdd(x.prof + role * 128 + 126, (unsigned long long)(clock64() - prof_t0));
+    atomicAdd(x.prof + role * 128 + 127, 1ull);
+  }
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    if (*x.abort_flag != 0) atomicCAS(p.status + 2, 0, *x.abort_flag);
+    if (*range_flag != 0) atomicOr(p.status, KDA_BIT_RANGE);
+  }
+  if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
+}
+
 }  // namespace u
 
 cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner) {
@@ -956,6 +1287,35 @@ cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_t
   if (blocks <= 0) return cudaSuccess;
   // Chained behind the planner by programmatic dependent launch when it directly follows it in the stream (function
   // of kda/b200/csrc/w3/base/cake/launch_m128.cu:37-60): the launch latency hides under the planner.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(u::THREADS);
+  cfg.dynamicSmemBytes = u::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = after_planner ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kerns[p.frontend ? 1 : 0][p.key_first ? 1 : 0], p, maps);
+}
+
+cudaError_t launch_chunk_dual(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner) {
+  typedef void (*Kern)(const ChunkParams, const TmaMaps);
+  static const Kern kerns[2][2] = {{u::kda_chunk_dual_kernel<0, 0>, u::kda_chunk_dual_kernel<0, 1>},
+                                   {u::kda_chunk_dual_kernel<1, 0>, u::kda_chunk_dual_kernel<1, 1>}};
+  static int attr_dev_mask = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_dev_mask & (1 << (dev & 31)))) {
+    for (int i = 0; i < 4; i++) {
+      cudaError_t e = cudaFuncSetAttribute(kerns[i >> 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize, u::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+    }
+    attr_dev_mask |= 1 << (dev & 31);
+  }
+  const long long blocks = (long long)n_task_cap * p.H;
+  if (blocks <= 0) return cudaSuccess;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
   cfg.blockDim = dim3(u::THREADS);

@@ -18,6 +18,8 @@ constexpr uint32_t TF_INIT_IDENTITY = 2u;  // start from S = I (transition chain
 constexpr uint32_t TF_V_ZERO = 4u;         // treat v as 0 (transition chain)
 constexpr uint32_t TF_OUT_AUX = 8u;        // write output rows to the auxiliary tensor (Qt)
 constexpr uint32_t TF_NO_OUT = 16u;        // do not write output rows
+constexpr uint32_t TF_DUAL = 64u;          // dual-chain kernel only: run chain L (this task's own flags, real v -> out, dst) AND
+                                           // chain Tr (S = I, v = 0 -> out_aux, dst2) over one operand preparation
 constexpr uint32_t TF_DST_VF = 32u;        // store the final state value-first whatever the launch's state layout
                                            // (transition maps: the scan applies them as  E <- E P)
 
@@ -29,7 +31,7 @@ struct __align__(16) Task {
   const float* src;    // initial state of head 0 (heads 16384 floats apart); unused with TF_INIT_*
   float* dst;          // final state of head 0, or nullptr
   void* ck;            // first checkpoint row of this run (head 0), or nullptr
-  long long pad_;
+  float* dst2;         // TF_DUAL: final state of the transition chain (head 0, always value-first); else unused
 };
 
 struct ChunkParams {

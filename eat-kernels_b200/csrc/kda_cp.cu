@@ -19,12 +19,16 @@ __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
     if (t1 < t0) t1 = t0;
     const size_t slot = (size_t)i * a.H * STATE_ELEMS;
     Task l, r;
-    l.t0 = t0; l.len = (int)(t1 - t0); l.flags = 0; l.src = nullptr; l.dst = a.S_loc + slot; l.ck = nullptr; l.pad_ = 0;
+    l.t0 = t0; l.len = (int)(t1 - t0); l.flags = 0; l.src = nullptr; l.dst = a.S_loc + slot; l.ck = nullptr; l.dst2 = nullptr;
     r = l;
     if (a.need_map[i]) {
       l.flags = TF_INIT_ZERO;
       r.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_OUT_AUX;
       r.dst = a.P + slot;
+      if (a.dual) {                       // both chains in one task: chain Tr's rows go to the auxiliary output, its map to dst2
+        l.flags |= TF_DUAL;
+        l.dst2 = a.P + slot;
+      }
     } else {
       if (a.src_base != nullptr) l.src = a.src_base + (size_t)i * a.src_stride;
       else l.flags = TF_INIT_ZERO;
@@ -34,11 +38,15 @@ __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
       l.flags |= TF_NO_OUT;
       r.flags |= TF_NO_OUT;
     }
-    a.tasks[2 * i] = l;
-    a.tasks[2 * i + 1] = r;
+    if (a.dual) {
+      a.tasks[i] = l;
+    } else {
+      a.tasks[2 * i] = l;
+      a.tasks[2 * i + 1] = r;
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    *a.n_tasks = 2 * a.n_seg;
+    *a.n_tasks = a.dual ? a.n_seg : 2 * a.n_seg;
     a.status[0] = 0; a.status[1] = 0; a.status[2] = 0; a.status[3] = 0;
   }
 }

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
     if (row >= 0)
       t.ck = a.ck_is_bf16 ? (void*)(reinterpret_cast<__nv_bfloat16*>(a.ck_base) + row * a.ck_row_stride)
                           : (void*)(reinterpret_cast<float*>(a.ck_base) + row * a.ck_row_stride);
-    t.pad_ = 0;
+    t.dst2 = nullptr;
     a.tasks_unsorted[i] = t;
   }
   __syncthreads();
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
         const int len = min(lp * C, t.len - q * lp * C);
         if (q < p - 1) {                                // chains L and Tr of a middle piece -> map slot m0 + q
           Task l;
-          l.t0 = t0; l.len = len; l.flags = TF_INIT_ZERO | TF_NO_OUT; l.src = nullptr; l.ck = nullptr; l.pad_ = 0;
+          l.t0 = t0; l.len = len; l.flags = TF_INIT_ZERO | TF_NO_OUT; l.src = nullptr; l.ck = nullptr; l.dst2 = nullptr;
           l.dst = a.map_L + (size_t)(m0 + q) * slot_elems;
           a.tasks[ia++] = l;
           l.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_NO_OUT | TF_DST_VF;
@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
           a.tasks[ia++] = l;
         }
         Task r;                                         // the piece itself, from its entering state
-        r.t0 = t0; r.len = len; r.flags = 0; r.pad_ = 0;
+        r.t0 = t0; r.len = len; r.flags = 0; r.dst2 = nullptr;
         r.src = (q == 1) ? a.map_L + (size_t)m0 * slot_elems : a.map_E + (size_t)(m0 + q - 1) * slot_elems;
         r.dst = (q == p - 1) ? t.dst : nullptr;
         r.ck = nullptr;

@@ -49,6 +49,8 @@ cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream);
 cudaError_t launch_scan_chains(const ScanChain* chains, const int* n_chains, int max_chains, const float* P, const float* L, float* E,
                                int H, int key_first, cudaStream_t stream);
 cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);    // mma.sync kernel
+// tcgen05 dual-chain kernel: tasks with TF_DUAL run chain L and the transition chain over one operand preparation
+cudaError_t launch_chunk_dual(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner = false);
 // tcgen05 kernel; after_planner: the launch directly follows launch_plan / launch_seg_plan in the stream and is chained
 // to it by programmatic dependent launch
 cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner = false);

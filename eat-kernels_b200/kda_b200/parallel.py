@@ -85,11 +85,14 @@ def plan_bounds(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fi
     return list(_plan(T, H, first_rank, n_sms, max_pieces, task_overhead, fixup_steps_per_chunk_head)[0])
 
 
+DUAL_COST = 1.76     # a dual-chain chunk step in units of a single-chain one (measured: 5.52 us vs 3.14 us)
+
+
 @functools.lru_cache(maxsize=256)        # the search costs milliseconds on the host; layouts repeat call after call
 def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_steps_per_chunk_head=0.0025):
     """Piece boundaries (chunk-aligned token offsets, first 0, last T) of one rank's shard, chosen by simulating the
-    segment launch: every mapped piece is two tasks per head (chains L and Tr), the first piece of the first rank one
-    plain task per head; a task costs its chunks plus `task_overhead` chunk steps, and mapped tokens cost a fix-up pass.
+    segment launch: on the first rank every mapped piece is two tasks per head (chains L and Tr) and the first piece one
+    plain task per head; on the other ranks every piece is mapped and is ONE dual-chain task per head (`DUAL_COST`); a task costs its chunks plus `task_overhead` chunk steps, and mapped tokens cost a fix-up pass.
     On the first rank the plain first piece may be LONGER than the mapped pieces: while its H CTAs run, the remaining
     SMs work through the doubled chains of the shorter pieces (with H = 96 on 148 SMs the plain chain alone would
     leave a third of the GPU idle)."""
@@ -107,7 +110,9 @@ def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_st
             pieces = [base + (1 if i < extra else 0) for i in range(m)]
             costs = [c_first + task_overhead] * H if c_first else []
             for c in pieces:
-                costs += [c + task_overhead] * (2 * H)
+                # first rank: the plain first piece keeps the launch on the single-chain kernel, a mapped piece is two
+                # tasks per head; other ranks: every piece is mapped and runs as one dual-chain task per head
+                costs += [c + task_overhead] * (2 * H) if first_rank else [DUAL_COST * c + task_overhead] * H
             cost = _makespan(costs, n_sms) + fixup_steps_per_chunk_head * rest * H
             if best_cost is None or cost < best_cost - 1e-9:
                 cuts, acc = [0], 0
@@ -148,10 +153,11 @@ def balanced_shards(T, world, H, n_sms=148, max_pieces=8):
 class CudaBackend:
     """The shipped backend: the three context-parallel steps on the current CUDA device through the C ABI."""
 
-    def __init__(self, kernel=None):
+    def __init__(self, kernel=None, dual=True):
         from . import default_kernel
         self.lib = _cabi.lib()
         self.kernel = default_kernel() if kernel is None else int(kernel)
+        self.dual = bool(dual)      # all-mapped segment launches run on the dual-chain kernel (False: two tasks per segment)
         self._table_cache = {}
 
     def _tables(self, bounds, need_map, dev):
@@ -200,7 +206,8 @@ class CudaBackend:
             a.src_base, a.src_slot_stride, a.src_slots = first_state.data_ptr(), first_state.stride(0), first_state.shape[0]
         a.workspace, a.workspace_bytes = (ws.data_ptr() + 255) // 256 * 256, ws_bytes
         a.status = status.data_ptr()
-        a.kernel = self.kernel
+        # all segments mapped (every rank but the first): one dual-chain task per segment and head
+        a.kernel = _cabi.KERNEL_TCGEN05_DUAL if (self.dual and self.kernel == _cabi.KERNEL_TCGEN05 and all(need_map)) else self.kernel
         s.n_seg = n
         s.seg_t0, s.seg_t1, s.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
         s.qt, s.P, s.S_loc = qt.data_ptr(), P.data_ptr(), S_loc.data_ptr()

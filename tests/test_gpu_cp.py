@@ -42,6 +42,34 @@ def test_context_parallel_single_gpu(kda, H, T, pieces, slow, kernel):
     ko.check_close(fin.cpu(), f2.cpu(), tag + " vs plain call (state)", 6e-3)
 
 
+@pytest.mark.parametrize("H,bounds,slow", [(4, [0, 500, 1000], False), (2, [0, 33, 64, 1000, 2047], True), (148, [0, 4096], False),
+                                           (3, [0, 1, 40], False)])
+def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow):
+    """A mapped segment as ONE task of the dual-chain kernel (both chains over one operand preparation) gives the
+    outputs, Qt rows and state maps of the two-task scheme (chain L and chain Tr as separate tasks): the same products
+    in the same order, so bit for bit; and the maps reproduce the plain chain's final state."""
+    from kda_b200 import parallel
+    T = bounds[-1]
+    inputs = ko.make_inputs_raw(H, [T], 50 + H)
+    if slow:
+        slow_gates_(inputs, 50)
+    q, k, v, g, beta, A_log, dt_bias, scale, init, _ = to_dev(inputs)
+    need = [1] * (len(bounds) - 1)
+    res = {}
+    for dual in (True, False):
+        be = parallel.CudaBackend(dual=dual)
+        res[dual] = [t.clone() for t in be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need, None)]
+        torch.cuda.synchronize()
+    for name, a, b in zip(("o_loc", "Qt", "P", "S_loc"), res[True], res[False]):
+        assert torch.equal(a, b), f"dual-chain {name} differs from the two-task scheme (H={H}, bounds={bounds})"
+    # compose the maps from the initial state and compare with the plain call's final state
+    S = init[0].double().cpu()
+    for i in range(len(need)):
+        S = S @ res[True][2][i].double().cpu() + res[True][3][i].double().cpu()
+    _, fin = kda.run(q, k, v, g, beta, A_log, dt_bias, scale, init, max_cut_pieces=0)
+    ko.check_close(S.float()[None], fin.cpu(), f"state through the dual-chain maps (H={H}, bounds={bounds})", 6e-3)
+
+
 def test_scan_matches_fp64(kda):
     from kda_b200 import parallel
     be = parallel.CudaBackend()
