@@ -463,6 +463,10 @@ def measure_longctx(args, world, rank, dev, steps, warmup, verify=True):
     parallel.context_parallel_prefill(q, k, v, g, beta, None, None, D ** -0.5, None, pieces=pieces, raw=False, backend=be, events=ev)
     torch.cuda.synchronize()
     phases = {b[0]: round(a[1].elapsed_time(b[1]), 4) for a, b in zip(ev[:-1], ev[1:])}
+    all_phases = [phases]
+    if world > 1:
+        all_phases = [None] * world
+        dist.all_gather_object(all_phases, phases)
     bounds = parallel.plan_bounds(T, H, rank == 0) if pieces <= 0 else parallel.split_pieces(T, pieces)
     mapped_tokens = T - (bounds[1] if rank == 0 else 0)
     fix_bytes = mapped_tokens * H * 3 * D * 2 + (len(bounds) - 1 - (1 if rank == 0 else 0)) * H * D * D * 4
@@ -482,7 +486,7 @@ def measure_longctx(args, world, rank, dev, steps, warmup, verify=True):
                      "frac": algo_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"]},
         "tensor": {"achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
                    "frac": flops / (ms * 1e-3) / 1e12 / pk["tf"]},
-        "phases_ms_rank0": phases,
+        "phases_ms_rank0": phases, "segments_ms_per_rank": [ph.get("segments") for ph in all_phases],
         "fixup": {"bytes": fix_bytes, "GB/s": (fix_bytes / (phases["fixup"] * 1e-3) / 1e9) if phases.get("fixup", 0) > 0 else None,
                   "note": "o_loc + Qt read, out written (768 B per mapped token-head) plus the entering states"},
         "clocks": clocks}
@@ -694,7 +698,7 @@ def main(argv=None):
         lc = measure_longctx(args, world, rank, dev, max(3, min(args.steps, 5)), 2, verify=not args.no_verify)
         if rank == 0:
             longctx = {kk: lc[kk] for kk in ("metric", "value", "unit", "ms_per_step", "steps", "config", "verification",
-                                               "verified", "roofline", "phases_ms_rank0", "fixup")}
+                                               "verified", "roofline", "phases_ms_rank0", "segments_ms_per_rank", "fixup")}
 
     if rank == 0:
         pk = peaks()

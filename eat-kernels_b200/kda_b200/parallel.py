@@ -153,12 +153,33 @@ def balanced_shards(T, world, H, n_sms=148, max_pieces=8):
 class CudaBackend:
     """The shipped backend: the three context-parallel steps on the current CUDA device through the C ABI."""
 
-    def __init__(self, kernel=None, dual=True):
+    def __init__(self, kernel=None, dual=True, reuse=False):
         from . import default_kernel
         self.lib = _cabi.lib()
         self.kernel = default_kernel() if kernel is None else int(kernel)
         self.dual = bool(dual)      # all-mapped segment launches run on the dual-chain kernel (False: two tasks per segment)
+        # reuse=True: every result and scratch tensor is allocated once per shape and handed out again at the next call
+        # (a serving loop over one layout then allocates nothing after its first step; results of a call are only
+        # valid until the next one)
+        self.reuse = bool(reuse)
+        self._bufs = {}
         self._table_cache = {}
+        self.status = None          # int32[4] of the most recent segment launch: [2] != 0 means a wait inside it gave up
+
+    def _buf(self, key, shape, dtype, dev, zero=False):
+        if not self.reuse:
+            return (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=dev)
+        k = (key, tuple(shape), dtype, str(dev))
+        t = self._bufs.get(k)
+        if t is None:
+            t = self._bufs[k] = (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=dev)
+        elif zero:
+            t.zero_()
+        return t
+
+    def kernel_error(self):
+        """Device-side error code of the most recent segment launch (0 = none); synchronises."""
+        return 0 if self.status is None else int(self.status[2].item())
 
     def _tables(self, bounds, need_map, dev):
         """Device copies of the piece tables, kept per layout: a repeated call uploads nothing."""
@@ -182,14 +203,16 @@ class CudaBackend:
         dev = q.device
         T, H = q.shape[1], q.shape[2]
         n = len(bounds) - 1
-        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device=dev)
-        qt = torch.empty(1, T, H, D, dtype=torch.bfloat16, device=dev)
-        P = torch.zeros(n, H, D, D, dtype=torch.float32, device=dev)
-        S_loc = torch.empty(n, H, D, D, dtype=torch.float32, device=dev)
+        out = self._buf("out", (1, T, H, D), torch.bfloat16, dev)
+        qt = self._buf("qt", (1, T, H, D), torch.bfloat16, dev)
+        # (the P of an unmapped piece must read as the zero map; mapped pieces overwrite theirs)
+        P = self._buf("P", (n, H, D, D), torch.float32, dev, zero=not all(need_map))
+        S_loc = self._buf("S_loc", (n, H, D, D), torch.float32, dev)
         t0, t1, nm = self._tables(bounds, need_map, dev)
         ws_bytes = self.lib.kda_prefill_workspace_bytes(2 * n, H)
-        ws = torch.zeros(ws_bytes + 256, dtype=torch.uint8, device=dev)
-        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        ws = self._buf("ws", (ws_bytes + 256,), torch.uint8, dev)
+        status = self._buf("status", (4,), torch.int32, dev)
+        self.status = status
         s = _cabi.KdaSegmentArgs()
         a = s.base
         a.q, a.k, a.v, a.g, a.beta, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), out.data_ptr()
@@ -218,8 +241,8 @@ class CudaBackend:
     def scan(self, P, S_loc, S0):
         """S_in[0] = S0 (or 0), S_in[i+1] = S_in[i] @ P[i] + S_loc[i]; returns (S_in [n,H,128,128], S_end [H,128,128])."""
         n, H = P.shape[0], P.shape[1]
-        S_in = torch.empty_like(S_loc)
-        S_end = torch.empty(H, D, D, dtype=torch.float32, device=P.device)
+        S_in = self._buf(("S_in", P.data_ptr()), tuple(S_loc.shape), torch.float32, P.device)
+        S_end = self._buf(("S_end", P.data_ptr()), (H, D, D), torch.float32, P.device)
         _cabi.check(self.lib.kda_scan_launch(P.data_ptr(), S_loc.data_ptr(), None if S0 is None else S0.data_ptr(),
                                              S_in.data_ptr(), S_end.data_ptr(), n, H, self._stream(P.device)), "kda_scan_launch")
         return S_in, S_end
@@ -352,8 +375,10 @@ def compose_rank_map(backend, P, S_loc):
     n = P.shape[0]
     _, L_rank = backend.scan(P, S_loc, None)
     if n == 1:
-        return P[0].clone(), L_rank
-    _, P_rank = backend.scan(P[1:], torch.zeros_like(S_loc[1:]), P[0].contiguous())
+        return P[0], L_rank
+    zeros = backend._buf("zeros", tuple(S_loc[1:].shape), torch.float32, P.device, zero=True) if hasattr(backend, "_buf") \
+        else torch.zeros_like(S_loc[1:])
+    _, P_rank = backend.scan(P[1:], zeros, P[0])
     return P_rank, L_rank
 
 
@@ -367,7 +392,10 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     piece boundaries by simulating the segment launch (`plan_bounds`); `pieces=n` cuts n equal pieces.
     `events`, when a list, receives (phase name, CUDA event) pairs recorded on the current stream at the phase
     boundaries ("start", "segments", "maps", "exchange", "scan", "fixup"), for callers that time the phases.
-    Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank)."""
+    Returns (out [1, T_local, H, 128] bf16 for the local tokens, final_state [1, H, 128, 128] fp32 on every rank).
+    Nothing here synchronises; `backend.kernel_error()` afterwards tells whether a bounded wait inside the segment
+    kernel gave up (the maps, and with them every rank's result, are then invalid).  With `CudaBackend(reuse=True)`
+    repeated calls over one layout allocate nothing after the first."""
     import torch.distributed as dist
 
     def mark(name):
@@ -403,10 +431,13 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     P_rank, L_rank = compose_rank_map(backend, P, S_loc)
     mark("maps")
     if world > 1:
-        mine = torch.stack([P_rank, L_rank])                               # [2, H, 128, 128]
-        gathered = torch.empty(world, *mine.shape, dtype=mine.dtype, device=mine.device)
-        dist.all_gather_into_tensor(gathered.view(world * 2, *mine.shape[1:]), mine, group=group)
-        S_in_ranks, S_final = backend.scan(gathered[:, 0].contiguous(), gathered[:, 1].contiguous(), None)
+        # two gathers straight into the layout the scan reads ([rank][H][128][128] each): no stacking, no copies
+        mk = backend._buf if hasattr(backend, "_buf") else (lambda key, shape, dt, dev, zero=False: torch.empty(shape, dtype=dt, device=dev))
+        gP = mk("gather_P", (world, H, D, D), P_rank.dtype, P_rank.device)
+        gL = mk("gather_L", (world, H, D, D), L_rank.dtype, L_rank.device)
+        dist.all_gather_into_tensor(gP.view(world * H, D, D), P_rank.contiguous(), group=group)
+        dist.all_gather_into_tensor(gL.view(world * H, D, D), L_rank.contiguous(), group=group)
+        S_in_ranks, S_final = backend.scan(gP, gL, None)
         S_enter = S_in_ranks[rank]
     else:
         S_enter = None
