@@ -6,6 +6,7 @@
 // (the algebra of kda/b200/csrc/w3/kernel.py:22-38 and kda/b200/csrc/w3/cp_fix.cu:4-21).  Both chains run as tasks of
 // the fused chunk kernel; this file plans those tasks, scans the maps and applies the output fix-up.
 #include "kda_cp.cuh"
+#include "kda_scan_tile.cuh"
 
 namespace kda {
 
@@ -57,55 +58,42 @@ cudaError_t launch_seg_plan(const SegPlanParams& a, cudaStream_t stream) {
 }
 
 // ------------------------------------------------------------------------------------------------ scan of the maps
-// S_in[0] = S0 (or 0);  S_in[i+1] = S_in[i] @ P[i] + S_loc[i].  Rows of S evolve independently, so a CTA carries
-// SCAN_ROWS value rows of one head through the whole chain in fp32 (P is re-read from L2 by the CTAs of a head).
-constexpr int SCAN_ROWS = 8;
-constexpr int SCAN_THREADS = 256;
-
-__global__ void __launch_bounds__(SCAN_THREADS) kda_scan_kernel(const float* __restrict__ P, const float* __restrict__ S_loc,
-                                                                const float* __restrict__ S0, float* __restrict__ S_in,
-                                                                float* __restrict__ S_end, int n_seg, int H) {
-  __shared__ float s_cur[SCAN_ROWS][D];
-  const int h = blockIdx.y, r0 = blockIdx.x * SCAN_ROWS;
-  const int tid = threadIdx.x, row = tid >> 5, lane = tid & 31;
+// S_in[0] = S0 (or 0);  S_in[i+1] = S_in[i] @ P[i] + S_loc[i].  Rows of S evolve independently, so a CTA carries 32
+// value rows of one head through the whole chain in fp32 as register tiles (kda_scan_tile.cuh).
+__global__ void __launch_bounds__(ST_THREADS) kda_scan_kernel(const float* __restrict__ P, const float* __restrict__ S_loc,
+                                                              const float* __restrict__ S0, float* __restrict__ S_in,
+                                                              float* __restrict__ S_end, int n_seg, int H) {
+  __shared__ __align__(16) ScanSmem sm;
+  const int h = blockIdx.y, tid = threadIdx.x;
+  const int r0 = blockIdx.x * ST_ROWS + 4 * (tid >> 5), c0 = 4 * (tid & 31);
   const size_t head_off = (size_t)h * STATE_ELEMS;
   const size_t seg_stride = (size_t)H * STATE_ELEMS;
-  float cur[4];
+  float cur[4][4];
+  if (S0 != nullptr) {
+    scan_tile_load(cur, S0 + head_off, r0, c0, 1);
+  } else {
 #pragma unroll
-  for (int j = 0; j < 4; j++) cur[j] = S0 ? S0[head_off + (size_t)(r0 + row) * D + lane + 32 * j] : 0.0f;
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) cur[i][j] = 0.0f;
+  }
   for (int i = 0; i < n_seg; i++) {
+    scan_tile_store(cur, S_in + i * seg_stride + head_off, r0, c0, 1);
+    float acc[4][4];
+    scan_tile_load(acc, S_loc + i * seg_stride + head_off, r0, c0, 1);
+    scan_tile_step(acc, cur, P + i * seg_stride + head_off, sm, tid);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      S_in[i * seg_stride + head_off + (size_t)(r0 + row) * D + lane + 32 * j] = cur[j];
-      s_cur[row][lane + 32 * j] = cur[j];
-    }
-    __syncthreads();
-    const float* Pi = P + i * seg_stride + head_off;
-    const float* Li = S_loc + i * seg_stride + head_off + (size_t)(r0 + row) * D;
-    float acc[4] = {Li[lane], Li[lane + 32], Li[lane + 64], Li[lane + 96]};
-#pragma unroll 8
-    for (int k = 0; k < D; k++) {
-      const float s = s_cur[row][k];
-      const float* pk = Pi + (size_t)k * D + lane;
-      acc[0] = fmaf(s, pk[0], acc[0]);
-      acc[1] = fmaf(s, pk[32], acc[1]);
-      acc[2] = fmaf(s, pk[64], acc[2]);
-      acc[3] = fmaf(s, pk[96], acc[3]);
-    }
-    __syncthreads();
+    for (int a = 0; a < 4; a++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) cur[j] = acc[j];
+      for (int b = 0; b < 4; b++) cur[a][b] = acc[a][b];
   }
-  if (S_end != nullptr) {
-#pragma unroll
-    for (int j = 0; j < 4; j++) S_end[head_off + (size_t)(r0 + row) * D + lane + 32 * j] = cur[j];
-  }
+  if (S_end != nullptr) scan_tile_store(cur, S_end + head_off, r0, c0, 1);
 }
 
 cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int n_seg, int H,
                         cudaStream_t stream) {
-  dim3 grid(D / SCAN_ROWS, H);
-  kda_scan_kernel<<<grid, SCAN_THREADS, 0, stream>>>(P, S_loc, S0, S_in, S_end, n_seg, H);
+  dim3 grid(D / ST_ROWS, H);
+  kda_scan_kernel<<<grid, ST_THREADS, 0, stream>>>(P, S_loc, S0, S_in, S_end, n_seg, H);
   return cudaGetLastError();
 }
 

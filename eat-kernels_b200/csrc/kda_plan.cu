@@ -14,6 +14,7 @@
 //          (kda/b200/csrc/w3/validate_dev.cuh:124-142): a sequence that lost its rows does not block later ones.
 #include "kda_common.cuh"
 #include "kda_plan.cuh"
+#include "kda_scan_tile.cuh"
 
 namespace kda {
 
@@ -399,57 +400,39 @@ cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream) {
 // Entering states of the pieces of every cut sequence: per chain and head  E[k] = E[k-1] applied to map k  with
 // E[-1] = the end state of piece 0.  In the value-first layout a state is [v][k] and a map acts as  E <- E P + L  (rows
 // v evolve independently); in the key-first layout the same relation reads  E[k'][v] = sum_k P[k][k'] E[k][v] + L[k'][v]
-// (columns v evolve independently; P is stored value-first in both cases).  A CTA carries eight independent rows /
-// columns of one head through the chain in fp32; P is read from L2 with coalesced rows.
-constexpr int SC_ROWS = 8, SC_THREADS = 256;
-
-__global__ void __launch_bounds__(SC_THREADS) kda_scan_chains_kernel(const ScanChain* __restrict__ chains, const int* __restrict__ n_chains,
+// (columns v evolve independently; P is stored value-first in both cases).  A CTA carries 32 independent rows /
+// columns of one head through the chain in fp32 as register tiles (kda_scan_tile.cuh).
+__global__ void __launch_bounds__(ST_THREADS) kda_scan_chains_kernel(const ScanChain* __restrict__ chains, const int* __restrict__ n_chains,
                                                                      const float* __restrict__ P, const float* __restrict__ L,
                                                                      float* __restrict__ E, int H, int kf) {
-  __shared__ float s_cur[SC_ROWS][D];
+  __shared__ __align__(16) ScanSmem sm;
   if ((int)blockIdx.z >= *n_chains) return;
   const ScanChain ch = chains[blockIdx.z];
   if (ch.count <= 0) return;
-  const int h = blockIdx.y, r0 = blockIdx.x * SC_ROWS;
-  const int tid = threadIdx.x, row = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, tid = threadIdx.x;
+  const int r0 = blockIdx.x * ST_ROWS + 4 * (tid >> 5), c0 = 4 * (tid & 31);
   const size_t head_off = (size_t)h * STATE_ELEMS, slot_stride = (size_t)H * STATE_ELEMS;
-  const int rs = kf ? 1 : D, ks = kf ? D : 1;       // element (independent index r, contracted / produced index k)
-  const size_t base = head_off + (size_t)(r0 + row) * rs;
-  float cur[4];
-#pragma unroll
-  for (int j = 0; j < 4; j++) cur[j] = ch.s0[base + (size_t)(lane + 32 * j) * ks];
+  const int ks = kf ? D : 1;            // stride of the contracted / produced index (the independent one has the other)
+  float cur[4][4];
+  scan_tile_load(cur, ch.s0 + head_off, r0, c0, ks);
   for (int i = 0; i < ch.count; i++) {
-    const size_t slot = (size_t)(ch.first + i) * slot_stride;
+    const size_t slot = (size_t)(ch.first + i) * slot_stride + head_off;
+    float acc[4][4];
+    scan_tile_load(acc, L + slot, r0, c0, ks);
+    scan_tile_step(acc, cur, P + slot, sm, tid);
 #pragma unroll
-    for (int j = 0; j < 4; j++) s_cur[row][lane + 32 * j] = cur[j];
-    __syncthreads();
-    const float* Pi = P + slot + head_off;
-    float acc[4];
+    for (int a = 0; a < 4; a++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[j] = L[slot + base + (size_t)(lane + 32 * j) * ks];
-#pragma unroll 8
-    for (int k = 0; k < D; k++) {
-      const float sv = s_cur[row][k];
-      const float* pk = Pi + (size_t)k * D + lane;
-      acc[0] = fmaf(sv, pk[0], acc[0]);
-      acc[1] = fmaf(sv, pk[32], acc[1]);
-      acc[2] = fmaf(sv, pk[64], acc[2]);
-      acc[3] = fmaf(sv, pk[96], acc[3]);
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      cur[j] = acc[j];
-      E[slot + base + (size_t)(lane + 32 * j) * ks] = cur[j];
-    }
+      for (int b = 0; b < 4; b++) cur[a][b] = acc[a][b];
+    scan_tile_store(cur, E + slot, r0, c0, ks);
   }
 }
 
 cudaError_t launch_scan_chains(const ScanChain* chains, const int* n_chains, int max_chains, const float* P, const float* L, float* E,
                                int H, int key_first, cudaStream_t stream) {
   if (max_chains <= 0) return cudaSuccess;
-  dim3 grid(D / SC_ROWS, H, max_chains);
-  kda_scan_chains_kernel<<<grid, SC_THREADS, 0, stream>>>(chains, n_chains, P, L, E, H, key_first);
+  dim3 grid(D / ST_ROWS, H, max_chains);
+  kda_scan_chains_kernel<<<grid, ST_THREADS, 0, stream>>>(chains, n_chains, P, L, E, H, key_first);
   return cudaGetLastError();
 }
 

@@ -85,7 +85,8 @@ def plan_bounds(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fi
     return list(_plan(T, H, first_rank, n_sms, max_pieces, task_overhead, fixup_steps_per_chunk_head)[0])
 
 
-DUAL_COST = 1.76     # a dual-chain chunk step in units of a single-chain one (measured: 5.52 us vs 3.14 us)
+DUAL_COST = 1.62     # a dual-chain chunk step in units of a single-chain one (measured inside the 131072-token segment
+                     # launches: 4.58 us against 2.82 us per chunk)
 
 
 @functools.lru_cache(maxsize=256)        # the search costs milliseconds on the host; layouts repeat call after call
@@ -98,7 +99,7 @@ def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_st
     leave a third of the GPU idle)."""
     nch = -(-T // CHUNK)
     if nch <= 1:
-        return [0, T], float(nch) + task_overhead
+        return [0, T], (float(nch) + task_overhead, 0.0)
     best, best_cost = [0, nch], None
     firsts = sorted({nch} | {max(1, int(nch * f / 16)) for f in range(1, 16)}) if first_rank else [0]
     for c_first in firsts:
@@ -113,41 +114,67 @@ def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_st
                 # first rank: the plain first piece keeps the launch on the single-chain kernel, a mapped piece is two
                 # tasks per head; other ranks: every piece is mapped and runs as one dual-chain task per head
                 costs += [c + task_overhead] * (2 * H) if first_rank else [DUAL_COST * c + task_overhead] * H
-            cost = _makespan(costs, n_sms) + fixup_steps_per_chunk_head * rest * H
-            if best_cost is None or cost < best_cost - 1e-9:
+            seg = _makespan(costs, n_sms)
+            fix = fixup_steps_per_chunk_head * rest * H
+            if best_cost is None or seg + fix < sum(best_cost) - 1e-9:
                 cuts, acc = [0], 0
                 for c in ([c_first] if c_first else []) + pieces:
                     acc += c
                     cuts.append(acc)
-                best, best_cost = cuts, cost
+                best, best_cost = cuts, (seg, fix)
     return [min(T, c * CHUNK) for c in best], best_cost
 
 
 def segment_cost(T, H, first_rank, n_sms=148, max_pieces=8):
-    """Simulated makespan of a rank's segment launch and fix-up, in chunk steps (see `plan_bounds`)."""
+    """Simulated makespan of a rank's segment launch plus its fix-up pass, in chunk steps (see `plan_bounds`)."""
+    return sum(phase_costs(T, H, first_rank, n_sms, max_pieces))
+
+
+def phase_costs(T, H, first_rank, n_sms=148, max_pieces=8):
+    """(segment launch, fix-up pass) of a rank's shard in chunk steps."""
     if T <= 0:
-        return 0.0
+        return 0.0, 0.0
     return _plan(T, H, first_rank, n_sms, max_pieces)[1]
 
 
 def balanced_shards(T, world, H, n_sms=148, max_pieces=8):
+    """Token counts per rank for a context-parallel call over `world` ranks (see `_balanced_shards`)."""
+    return list(_balanced_shards(T, world, H, n_sms, max_pieces))
+
+
+@functools.lru_cache(maxsize=64)         # about a second of host search for a new (T, world, H); layouts repeat
+def _balanced_shards(T, world, H, n_sms, max_pieces):
     """Token counts per rank (chunk-aligned, in rank order, summing to T) for context parallelism.  Rank 0 runs the plain
-    chain on its first piece while every other piece runs two chains, so equal shards leave rank 0 idle; the shards
-    are sized inversely to each rank's cost per chunk in the wave model (the reference cuts unequal segments for the
-    same reason, kda/b200/csrc/w3/kernel.py:22-38)."""
+    chain on its first piece while every other piece runs two chains, so equal shards leave rank 0 idle (the reference
+    cuts unequal segments for the same reason, kda/b200/csrc/w3/kernel.py:22-38).  The exchange of the maps stands
+    between the segment launches and the fix-up passes of all ranks, so the call lasts
+    max over ranks (segments) + max over ranks (fix-up); the first shard is the one that minimises that sum in the wave
+    model, the other ranks share the rest equally."""
     nch = -(-T // CHUNK)
     if world <= 1 or nch < world:
-        return [T] + [0] * (world - 1)
-    eq = nch // world
-    inv = []
-    for r in range(world):
-        inv.append(eq / max(1, segment_cost(eq * CHUNK, H, r == 0, n_sms, max_pieces)))
-    tot = sum(inv)
-    chunks = [max(1, int(nch * x / tot)) for x in inv]
-    chunks[0] += nch - sum(chunks)
+        return (T,) + (0,) * (world - 1)
+
+    def split(c0):
+        rest = nch - c0
+        base, extra = divmod(rest, world - 1)
+        return [c0] + [base + (1 if i < extra else 0) for i in range(world - 1)]
+
+    def cost(c0):
+        ch = split(c0)
+        ph = [phase_costs(ch[0] * CHUNK, H, True, n_sms, max_pieces), phase_costs(ch[1] * CHUNK, H, False, n_sms, max_pieces)]
+        return max(x[0] for x in ph) + max(x[1] for x in ph)
+
+    # coarse scan of the first shard between the equal share and the whole sequence, then a local refinement
+    lo, hi = nch // world, nch - (world - 1)
+    step = max(1, (hi - lo) // 48)
+    best = min(range(lo, hi + 1, step), key=cost)
+    while step > 1:
+        step = max(1, step // 4)
+        best = min(range(max(lo, best - 4 * step), min(hi, best + 4 * step) + 1, step), key=cost)
+    chunks = split(best)
     shards = [c * CHUNK for c in chunks]
     shards[-1] -= nch * CHUNK - T          # the last chunk of the sequence may be partial
-    return shards
+    return tuple(shards)
 
 
 class CudaBackend:
