@@ -56,11 +56,11 @@ constexpr int OFF_KIS = OFF_RAW + 2 * RAW_STAGE;              // 2 x 8192 (one p
 constexpr int OFF_TBH = OFF_KIS + 2 * 8192;                   // 2 x 2048 (bf16, 64-byte swizzle)
 constexpr int OFF_L = OFF_TBH + 4096;                         // 2 x 4096 fp32 [32][32]
 constexpr int OFF_DEC = OFF_L + 8192;                         // 4 x 512 (a slot is rewritten four chunks later)
-constexpr int OFF_FR = OFF_DEC + 2048;                        // per prep group: r, 2^r, 2^(G31-r) : 2 x 3 x 512
+constexpr int OFF_FR = OFF_DEC + 2048;                        // per prep group: (free), 2^r, first-half sum then 2^(G31-r) : 2 x 3 x 512
 constexpr int OFF_BETA = OFF_FR + 2 * 1536;                   // raw-stage beta: 2 x 128
 constexpr int OFF_LBETA = OFF_BETA + 256;                     // beta next to L: 2 x 128
 constexpr int OFF_BAR = OFF_LBETA + 256;                      // mbarriers
-constexpr int NUM_BARS = 34;
+constexpr int NUM_BARS = 42;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // +0 tmem slot, +8 abort code, +12 range flag, +16 wait limit (ns)
 constexpr int SMEM_BYTES = OFF_MISC + 64;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -69,7 +69,8 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
               B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20, B_V_EMPTY = 21,
               B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29,
-              B_MMA1_DONE_T = 31, B_S_READY_T = 32;   // second chain of the dual-chain kernel
+              B_MMA1_DONE_T = 31, B_S_READY_T = 32,   // second chain of the dual-chain kernel
+              B_TOT = 34;                             // 2 groups x 4 warp pairs: first-half sums of step A
 
 // tensor-memory columns
 constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
@@ -262,44 +263,62 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
       if (FE == 1) {
         const float* g = reinterpret_cast<const float*>(raw + RAW_G);
 #pragma unroll
-        for (int i = 0; i < 16; i++) a[i] = g[(16 * half + i) * D + ch] * LOG2E;
+        for (int i = 0; i < 16; i++) a[i] = g[(16 * half + i) * D + ch];
       } else {
         // log2-decay = lower_bound log2(e) sigmoid(x), x = exp(A_log) (g + dt_bias); sigmoid(x) = 1 / (1 + 2^(-x log2 e))
         // with the exponent argument formed by one fused multiply-add per element
         const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(raw + RAW_G);
-        const float c2 = p.lower_bound * LOG2E;
         const float m1 = -LOG2E * eA, m0 = m1 * dtb;
 #pragma unroll
-        for (int i = 0; i < 16; i++) a[i] = c2 * rcpf(1.0f + ex2f(fmaf(__bfloat162float(g[(16 * half + i) * D + ch]), m1, m0)));
+        for (int i = 0; i < 16; i++) a[i] = rcpf(1.0f + ex2f(fmaf(__bfloat162float(g[(16 * half + i) * D + ch]), m1, m0)));
       }
+      if (nvalid < C) {                       // rows of the next sequence (last chunk only): no decay
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
-        if (16 * half + i >= nvalid) a[i] = 0.0f;
-        if (i > 0) a[i] += a[i - 1];
+        for (int i = 0; i < 16; i++)
+          if (16 * half + i >= nvalid) a[i] = 0.0f;
       }
-      if (half == 0) tot[ch] = a[15];
-      PROF_STAMP(2, 10);
-      named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: G may now overwrite them in place
-      PROF_STAMP(2, 11);
-      // Every warp of the group has left the previous chunk (step C reads beta_s), so beta may be replaced only now.
-      if (ptid < C) {
-        beta_s[ptid] = beta_next;
-        if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
+      // inclusive cumulative sum in log2 units, the unit conversion fused into the additions
+      const float unit = (FE == 1) ? LOG2E : p.lower_bound * LOG2E;
+      a[0] *= unit;
+#pragma unroll
+      for (int i = 1; i < 16; i++) a[i] = fmaf(a[i], unit, a[i - 1]);
+      if (FE == 1) {
+        // fp32 gates are replaced in place by the thread that read them, so only the first-half sums cross threads:
+        // warp pw hands the sums of its 32 channels to warp pw + 4 through a barrier of their own.
+        if (half == 0) {
+          tot[ch] = a[15];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(x.bar(B_TOT + 4 * grp + pw));
+        } else {
+          x.wait(B_TOT + 4 * grp + (pw - 4), par, E_PREP);
+        }
+        PROF_STAMP(2, 10);
+        PROF_STAMP(2, 11);
+      } else {
+        if (half == 0) tot[ch] = a[15];
+        PROF_STAMP(2, 10);
+        named_bar_sync(bar_id, PREP_THREADS);   // all raw g values are in registers: the exponents may now overwrite the tile
+        PROF_STAMP(2, 11);
       }
+      // What step B needs is the exponent relative to r = G after token 15, clamped to the representable range:
+      // tokens 0-15 have G - r = own sum - r >= 0, tokens 16-31 have G - r = their own partial sum <= 0.
       if (half == 1) {
         const float r = tot[ch];
-        // Range of the primed operands: their exponents are taken relative to the decay after token 15, so the largest
-        // ones belong to token 0 (at most -r) and token 31 (a[15], still the second half's own sum here).  Beyond
-        // 2^126 they are clamped below and the intra-chunk products of this chunk are no longer exact: report it.
-        // (Checked here, by the threads that hold both numbers anyway, and reported by one lane per warp: these warps
-        // set the pace of the kernel, and a separate test in the first half of step A cost 2.7 % of it.)
+        // Range of the primed operands: the largest exponents belong to token 0 (at most -r) and token 31 (a[15], the
+        // second half's own sum).  Beyond 2^126 they are clamped and the intra-chunk products of this chunk are no
+        // longer exact: report it.  (Checked here, by the threads that hold both numbers anyway, and reported by one
+        // lane per warp: these warps set the pace of the kernel, and a separate test in the first half of step A cost
+        // 2.7 % of it.)
         if (__any_sync(0xffffffffu, fminf(r, a[15]) < -126.0f) && lane == 0) *range_flag = 1;
-#pragma unroll
-        for (int i = 0; i < 16; i++) a[i] += r;
-        fr[ch] = r;
         fer[ch] = ex2f(r);
-        dec[ch] = ex2f(a[15]);
-        tot[ch] = ex2f(a[15] - r);      // 2^(G31 - r), read back below as the kr factor
+        dec[ch] = ex2f(a[15] + r);
+        tot[ch] = ex2f(a[15]);          // 2^(G31 - r), read back below as the kr factor
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] = fmaxf(a[i], -126.0f);
+      } else {
+        const float r = a[15];
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] = fminf(a[i] - r, 126.0f);
       }
 #pragma unroll
       for (int i = 0; i < 16; i++) Gsm[(16 * half + i) * D + ch] = a[i];
@@ -307,6 +326,12 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     PROF_STAMP(2, 12);
     named_bar_sync(bar_id, PREP_THREADS);
     PROF_STAMP(2, 26);
+    // Every warp of the group has left the previous chunk (step C reads beta_s), so beta may be replaced only now; step
+    // C of this chunk reads it after the next barrier.
+    if (ptid < C) {
+      beta_s[ptid] = beta_next;
+      if (c + PREP_GROUPS < x.nchunks) beta_next = load_beta<FE>(p, x, c + PREP_GROUPS, ptid);
+    }
 
     // ---- B: L2 norm and decayed operand tiles; a warp owns 4 tokens, a lane 4 channels.  [kd ; qd] is written as
     // soon as MMA1 of the chunk two back has read the stage; kr waits in registers until MMA3 has released the rest.
@@ -315,10 +340,8 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
     PROF_STAMP(2, 14);
     float krr[4][4];
     {
-      const float4 r4 = *reinterpret_cast<const float4*>(fr + 4 * lane);
       const float4 er4 = *reinterpret_cast<const float4*>(fer + 4 * lane);
       const float4 elr4 = *reinterpret_cast<const float4*>(tot + 4 * lane);
-      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
       const float er[4] = {er4.x, er4.y, er4.z, er4.w};
       const float elr[4] = {elr4.x, elr4.y, elr4.z, elr4.w};
 #pragma unroll
@@ -327,7 +350,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         const uint32_t off = rawtile_off(tok, 4 * lane);
         uint2 q2 = *reinterpret_cast<const uint2*>(raw + RAW_Q + off);
         uint2 k2 = *reinterpret_cast<const uint2*>(raw + RAW_K + off);
-        if (tok >= nvalid) { q2 = make_uint2(0u, 0u); k2 = make_uint2(0u, 0u); }   // rows of the next sequence
+        if (nvalid < C && tok >= nvalid) { q2 = make_uint2(0u, 0u); k2 = make_uint2(0u, 0u); }   // rows of the next sequence
         const float qf[4] = {bf16_lo(q2.x), bf16_hi(q2.x), bf16_lo(q2.y), bf16_hi(q2.y)};
         const float kf[4] = {bf16_lo(k2.x), bf16_hi(k2.x), bf16_lo(k2.y), bf16_hi(k2.y)};
         float qinv = p.scale, kinv = 1.0f;
@@ -347,8 +370,7 @@ __device__ void role_prep(const ChunkParams& p, const Ctx& x, int grp, int ptid)
         float kds[4], qds[4], kis[4], kdt[4], qdt[4];
 #pragma unroll
         for (int j = 0; j < 4; j += 2) {               // channel pairs, packed fp32x2 arithmetic
-          const float e0 = fminf(fmaxf(Gv[j] - rr[j], -126.0f), 126.0f);
-          const float e1 = fminf(fmaxf(Gv[j + 1] - rr[j + 1], -126.0f), 126.0f);
+          const float e0 = Gv[j], e1 = Gv[j + 1];
           const float2 E = make_float2(ex2f(e0), ex2f(e1)), Ei = make_float2(ex2f(-e0), ex2f(-e1));
           float2 kn = make_float2(kf[j], kf[j + 1]);
           if (FE == 0) kn = mul2(kn, make_float2(kinv, kinv));
@@ -807,9 +829,14 @@ __device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, 
     if (!(task.flags & TF_NO_OUT)) {
       const int nvalid = min(C, x.len - c * C);
       __nv_bfloat16* orow = obase + (x.t0 + (long long)c * C + 16 * hf) * p.ldo;
+      if (nvalid == C) {
 #pragma unroll
-      for (int i = 0; i < 16; i++)
-        if (16 * hf + i < nvalid) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
+        for (int i = 0; i < 16; i++) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+          if (16 * hf + i < nvalid) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
+      }
     }
   }
 }
@@ -892,6 +919,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
     mbar_init(x.bar(B_MMA1_DONE), 1);
     mbar_init(x.bar(B_S_READY), 8);
     mbar_init(x.bar(B_DRAIN), 1);
+    for (int i = 0; i < 8; i++) mbar_init(x.bar(B_TOT + i), 1);
     fence_barrier_init();
   }
   if (warp == W_MMA) {
@@ -1223,6 +1251,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
     mbar_init(x.bar(B_MMA1_DONE_T), 1);
     mbar_init(x.bar(B_S_READY_T), 8);
     mbar_init(x.bar(B_DRAIN), 1);
+    for (int i = 0; i < 8; i++) mbar_init(x.bar(B_TOT + i), 1);
     fence_barrier_init();
   }
   if (warp == W_MMA) {
