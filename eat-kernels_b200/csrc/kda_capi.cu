@@ -77,7 +77,7 @@ int sm_count() {
 int check_tokens(const KdaPrefillArgs* a) {
   if (a == nullptr) return KDA_ERR_ARG;
   if (a->H <= 0 || a->N < 0 || a->T < 0) return KDA_ERR_ARG;
-  if (a->kernel != KDA_KERNEL_TCGEN05 && a->kernel != KDA_KERNEL_MMA_SYNC && a->kernel != KDA_KERNEL_TCGEN05_DUAL) return KDA_ERR_ARG;
+  if (a->kernel != KDA_KERNEL_TCGEN05 && a->kernel != KDA_KERNEL_MMA_SYNC && a->kernel != KDA_KERNEL_TCGEN05_TWO_TASK) return KDA_ERR_ARG;
   if (a->frontend != KDA_FRONTEND_RAW && a->frontend != KDA_FRONTEND_PLAIN) return KDA_ERR_ARG;
   if (a->state_layout != KDA_STATE_VALUE_FIRST && a->state_layout != KDA_STATE_KEY_FIRST) return KDA_ERR_ARG;
   if (a->T > 0) {
@@ -208,6 +208,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   pl.trash = w.trash; pl.cu_safe = w.cu_safe; pl.tasks_unsorted = w.tasks_unsorted; pl.tasks = w.tasks;
   pl.n_tasks = w.n_tasks; pl.status = a->status;
   pl.max_pieces = pieces; pl.n_sm = sm_count(); pl.key_first = a->state_layout == KDA_STATE_KEY_FIRST;
+  pl.dual = a->kernel != KDA_KERNEL_MMA_SYNC;
   if (pieces > 0) {
     pl.tasks_b = w.tasks_b; pl.n_tasks_b = w.n_tasks + 1; pl.n_chains = w.n_tasks + 2; pl.chains = w.chains;
     pl.map_P = w.map_P; pl.map_L = w.map_L; pl.map_E = w.map_E;
@@ -229,7 +230,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
     if (rc != KDA_OK) return rc;
   }
   // first launch: every uncut sequence (or all of them), piece 0 and the map chains of the cut ones
-  e = umma ? kda::launch_chunk_umma(p, maps, a->N + 2 * pieces, stream, true) : kda::launch_chunk_fwd(p, a->N + 2 * pieces, stream);
+  e = umma ? kda::launch_chunk_umma(p, maps, a->N + 2 * pieces, stream) : kda::launch_chunk_fwd(p, a->N + 2 * pieces, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   if (pieces > 0) {
     // entering states of the later pieces, then those pieces (both launches find nothing to do when nothing was cut)
@@ -305,7 +306,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   sp.need_map = s->seg_need_map;
   sp.src_base = a->src_base; sp.src_stride = a->src_slot_stride;
   sp.no_out = maps_only ? 1 : 0;
-  sp.dual = a->kernel == KDA_KERNEL_TCGEN05_DUAL;  // a mapped segment as one dual-chain task instead of two tasks
+  sp.dual = a->kernel == KDA_KERNEL_TCGEN05;       // a mapped segment as one dual-chain task instead of two tasks
   sp.P = s->P; sp.S_loc = s->S_loc;
   sp.tasks = w.tasks; sp.n_tasks = w.n_tasks; sp.status = a->status;
   cudaError_t e = kda::launch_seg_plan(sp, stream);
@@ -322,7 +323,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
     kda::TmaMaps maps;
     rc = fill_tma_maps(maps, a);
     if (rc != KDA_OK) return rc;
-    e = sp.dual ? kda::launch_chunk_dual(p, maps, s->n_seg, stream, true) : kda::launch_chunk_umma(p, maps, 2 * s->n_seg, stream, true);
+    e = kda::launch_chunk_umma(p, maps, sp.dual ? s->n_seg : 2 * s->n_seg, stream);
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return KDA_OK;

@@ -69,11 +69,12 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr int B_G_FULL = 0, B_G_EMPTY = 2, B_CONS_EMPTY = 4, B_P1_FULL = 6, B_INV_FULL = 8, B_L_FULL = 10,
               B_L_EMPTY = 12, B_O_FULL = 14, B_O_EMPTY = 16, B_MMA1_DONE = 18, B_S_READY = 19, B_DRAIN = 20, B_V_EMPTY = 21,
               B_QK_FULL = 23, B_QK_EMPTY = 25, B_V_FULL = 27, B_KDQD_EMPTY = 29,
-              B_MMA1_DONE_T = 31, B_S_READY_T = 32,   // second chain of the dual-chain kernel
+              B_MMA1_DONE_T = 31, B_S_READY_T = 32,   // second chain of a dual-chain task
               B_TOT = 34;                             // 2 groups x 4 warp pairs: first-half sums of step A
 
 // tensor-memory columns
 constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_WO = 128, TM_U = 256;
+constexpr uint32_t TD_S0 = 0, TD_S1 = 128, TD_WO0 = 256, TD_WO1 = 320, TD_U0 = 384, TD_U1 = 448;   // dual-chain tasks
 
 // error codes written to status[2] when a bounded wait gives up (which role, which barrier)
 constexpr int E_LOAD = 0x40, E_PREP = 0x80, E_INV = 0xc0, E_MMA = 0x100, E_SCALE = 0x140, E_EPI = 0x180, E_DRAIN = 0x1c0;
@@ -841,147 +842,23 @@ __device__ void role_tmem(const ChunkParams& p, const Task& task, const Ctx& x, 
   }
 }
 
-// ------------------------------------------------------------------------------------------------ kernel
-template <int FE, int KF>
-__global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int warp = tid >> 5;
-  const int H = p.H;
-  const int rank = blockIdx.x / H, h = blockIdx.x % H;
-
-  // Launched as a programmatic dependent of the planner (its CTAs become resident while the planner still runs): wait
-  // here until the planner's writes (status, task table) are visible.  A no-op for an ordinary launch.
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  if (p.status[0] & 1) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
-    const long long rows = p.T * H;
-    for (long long r = blockIdx.x; r < rows; r += gridDim.x)
-      if (tid < 16) reinterpret_cast<uint4*>(p.out + (r / H) * p.ldo + (r % H) * D)[tid] = make_uint4(0, 0, 0, 0);
-  }
-  if (rank >= *p.n_tasks) return;
-  const Task task = p.tasks[rank];
-  Ctx x;
-  x.smem = smem;
-  x.bars = smem_u32(smem + OFF_BAR);
-  x.abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
-  x.h = h;
-  x.len = task.len;
-  x.nchunks = (task.len + C - 1) / C;
-  x.t0 = task.t0;
-#ifdef KDA_PROF
-  x.prof = p.prof;
-  const long long prof_t0 = clock64();
-#endif
-
-  if (x.nchunks == 0) {
-    // empty run: the state passes through (source -> destination) without touching tensor memory
-    if (task.dst != nullptr) {
-      float* dst = task.dst + (size_t)h * STATE_ELEMS;
-      const float* src = (task.flags & (TF_INIT_ZERO | TF_INIT_IDENTITY)) ? nullptr : task.src + (size_t)h * STATE_ELEMS;
-      if (src != dst) {
-        for (int i = tid; i < STATE_ELEMS / 4; i += THREADS) {
-          float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (src != nullptr) f = reinterpret_cast<const float4*>(src)[i];
-          else if (task.flags & TF_INIT_IDENTITY) {
-            const int row = (4 * i) / D, col = (4 * i) % D;
-            f = make_float4(row == col ? 1.f : 0.f, row == col + 1 ? 1.f : 0.f, row == col + 2 ? 1.f : 0.f, row == col + 3 ? 1.f : 0.f);
-          }
-          reinterpret_cast<float4*>(dst)[i] = f;
-        }
-      }
-    }
-    return;
-  }
-
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
-  volatile int* range_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 12);
-  if (tid == 0) {
-    *x.abort_flag = 0;
-    *range_flag = 0;
-    *reinterpret_cast<volatile unsigned long long*>(smem + OFF_MISC + 16) = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
-    for (int i = 0; i < 2; i++) {
-      mbar_init(x.bar(B_G_FULL + i), 1);
-      mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
-      mbar_init(x.bar(B_QK_FULL + i), 1);
-      mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
-      // diagnostic switch: the v barriers expect one arrival more than they will ever get, so their waiters give up
-      mbar_init(x.bar(B_V_FULL + i), (p.debug_flags & DBG_STALL_V_STREAM) ? 2 : 1);
-      mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
-      mbar_init(x.bar(B_CONS_EMPTY + i), 1);
-      mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
-      mbar_init(x.bar(B_INV_FULL + i), 1);
-      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
-      mbar_init(x.bar(B_V_EMPTY + i), 1);
-      mbar_init(x.bar(B_L_EMPTY + i), 1);
-      mbar_init(x.bar(B_O_FULL + i), 1);
-      mbar_init(x.bar(B_O_EMPTY + i), 8);
-    }
-    mbar_init(x.bar(B_MMA1_DONE), 1);
-    mbar_init(x.bar(B_S_READY), 8);
-    mbar_init(x.bar(B_DRAIN), 1);
-    for (int i = 0; i < 8; i++) mbar_init(x.bar(B_TOT + i), 1);
-    fence_barrier_init();
-  }
-  if (warp == W_MMA) {
-    tmem_alloc(smem_u32(tmem_slot), TM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const bool v_zero = (task.flags & TF_V_ZERO) != 0;
-
-  if (warp == W_MMA) {
-    role_mma(x, tmem, v_zero);
-    __syncwarp();
-  } else if (warp == W_INV0 || warp == W_INV0 + 1) {
-    role_inverse(x, warp - W_INV0, lane);
-  } else if (warp == W_LOAD) {
-    role_loader<FE>(p, maps, x, lane);
-    __syncwarp();
-  } else if (warp < W_PREP0) {
-    role_tmem<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
-  } else {
-    const int pt = tid - W_PREP0 * 32;
-    role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
-  }
-
-#ifdef KDA_PROF
-  if (lane == 0 && blockIdx.x == 0 && x.prof != nullptr) {
-    const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_PREP0 ? 5 : 2)));
-    atomicAdd(x.prof + role * 128 + 126, (unsigned long long)(clock64() - prof_t0));
-    atomicAdd(x.prof + role * 128 + 127, 1ull);
-  }
-#endif
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    if (*x.abort_flag != 0) atomicCAS(p.status + 2, 0, *x.abort_flag);
-    if (*range_flag != 0) atomicOr(p.status, KDA_BIT_RANGE);
-  }
-  if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
-}
-
-// ================================================================================================ dual-chain kernel
-// Context parallelism needs, for a token segment whose entering state is not known yet, TWO chains over the same tokens:
-// chain L from S = 0 with the real v (o_loc, S_loc) and chain Tr from S = I with v = 0 (Qt, P).  Everything the
-// preparation warps, the loader and the inverse warps produce is the same for both, and the tensor pipe is busy a
-// quarter of the time, so one task runs both chains over ONE operand preparation: a second state in tensor-memory
-// columns 128-255, each MMA group issued twice, the tensor-memory warps serving both states (function of the reference's
-// dual kernel, kda/b200/csrc/w3/base/cake_dual/kda_m128.cu:821-823, kda/b200/csrc/w3/base/dual.py:1-4).
-// A kernel of its own (the single-chain kernel above is untouched): tasks with TF_DUAL run both chains, the others one.
+// ================================================================================================ dual-chain tasks
+// Context parallelism and the cuts of long sequences need, for a token segment whose entering state is not known yet,
+// TWO chains over the same tokens: chain L from S = 0 with the real v (o_loc, S_loc) and chain Tr from S = I with v = 0
+// (Qt, P).  Everything the preparation warps, the loader and the inverse warps produce is the same for both, and the
+// tensor pipe is busy a quarter of the time, so a task flagged TF_DUAL runs both chains over ONE operand preparation: a
+// second state in tensor-memory columns 128-255, each MMA group issued twice, the tensor-memory warps serving both
+// states (function of the reference's dual kernel, kda/b200/csrc/w3/base/cake_dual/kda_m128.cu:821-823,
+// kda/b200/csrc/w3/base/dual.py:1-4).  The issuer and the tensor-memory warps have roles of their own for such a task
+// (chosen once per CTA, so a launch mixes plain and dual tasks at no cost to the plain ones); the other roles do not
+// know the difference.
 // Tensor memory of a dual task: S_L 0-127, S_T 128-255, [W | O] of L 256-319, of T 320-383 (one buffer per chain: the
-// other chain's work hides the read-out), U of L 384-447, of T 448-511 (two stages each).  A single-chain task in this
-// kernel keeps the single-chain kernel's map for [W | O] (columns 128-255, one buffer per stage): with one buffer the
-// read-out of O would sit on its serial chain (measured: 37 % slower).
-constexpr uint32_t TD_S0 = 0, TD_S1 = 128, TD_WO0 = 256, TD_WO1 = 320, TD_U0 = 384, TD_U1 = 448;
+// other chain's work hides the read-out), U of L 384-447, of T 448-511 (two stages each).
 
-__device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any, bool dual_any) {
+__device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any) {
   const uint32_t go = elect_one();
   const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_any, 0);
   const bool v_zero = __shfl_sync(0xffffffffu, (int)v_zero_any, 0) != 0;
-  const bool dual = __shfl_sync(0xffffffffu, (int)dual_any, 0) != 0;
   const int nchunks = __shfl_sync(0xffffffffu, x.nchunks, 0);
   const uint32_t sb = smem_u32(x.smem);
   constexpr uint32_t ID1 = make_idesc(FMT_TF32, 128, 64, 0, 0, 0);
@@ -997,7 +874,7 @@ __device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any, 
   const uint64_t d_m = make_sdesc(sb + OFF_CONS + CS_M, 16, 1024, LAYOUT_SW128);
   const uint32_t tS0 = tmem + TD_S0, tS1 = tmem + TD_S1, tWO1 = tmem + TD_WO1;
   x.wait(B_S_READY, 0, E_MMA, 0);                  // initial states are in tensor memory
-  if (dual) x.wait(B_S_READY_T, 0, E_MMA, 0);
+  x.wait(B_S_READY_T, 0, E_MMA, 0);
 #pragma unroll 1
   for (int c = 0; c < nchunks; c++) {
     const int s = c & 1;
@@ -1005,24 +882,21 @@ __device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any, 
     const uint64_t so = (uint64_t)(s * (CS_STAGE >> 4));
     const uint64_t so_tbh = (uint64_t)(s * (2048 >> 4));
     const uint32_t tU0 = tmem + TD_U0 + 32 * s, tU1 = tmem + TD_U1 + 32 * s;
-    // chain L's [W | O]: per chain (one phase per chunk) in a dual task, per stage as in the single-chain kernel else
-    const uint32_t tWO0 = dual ? tmem + TD_WO0 : tmem + TM_WO + 64 * s;
-    const int ob0 = dual ? 0 : s;
+    // [W | O]: one buffer per chain (one phase per chunk), not per stage as in the single-chain role
+    const uint32_t tWO0 = tmem + TD_WO0;
     x.wait(B_P1_FULL + s, par, E_MMA, 0);
-    x.wait(B_O_EMPTY + ob0, (dual ? cpar : par) ^ 1, E_MMA, 0);
+    x.wait(B_O_EMPTY + 0, cpar ^ 1, E_MMA, 0);
     tc_fence_after();
 #pragma unroll
     for (int ks = 0; ks < 16; ks++)
       mma_ts_tf32_pred(tWO0, tS0 + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
     mma_commit_pred(x.bar(B_MMA1_DONE), go);
-    if (dual) {
-      x.wait(B_O_EMPTY + 1, cpar ^ 1, E_MMA, 0);
-      tc_fence_after();
+    x.wait(B_O_EMPTY + 1, cpar ^ 1, E_MMA, 0);
+    tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < 16; ks++)
-        mma_ts_tf32_pred(tWO1, tS1 + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
-      mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
-    }
+    for (int ks = 0; ks < 16; ks++)
+      mma_ts_tf32_pred(tWO1, tS1 + 8 * ks, d_kdqd + so + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), ID1, ks > 0, go);
+    mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
     mma_commit_pred(x.bar(B_KDQD_EMPTY + s), go);
     x.wait(B_INV_FULL + s, par, E_MMA, 0);
     x.wait(B_V_FULL + s, par, E_MMA, 0);
@@ -1035,38 +909,32 @@ __device__ void role_mma_dual(const Ctx& x, uint32_t tmem_any, bool v_zero_any, 
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
       mma_ts_tf32_pred(tU0, tWO0 + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, (ks > 0) || !v_zero, go);
-    if (dual) {
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++)                      // the transition chain has v = 0: U = - W Tb^T
-        mma_ts_tf32_pred(tU1, tWO1 + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, ks > 0, go);
-    }
+    for (int ks = 0; ks < 4; ks++)                      // the transition chain has v = 0: U = - W Tb^T
+      mma_ts_tf32_pred(tU1, tWO1 + 8 * ks, d_tb + so + (uint64_t)((ks * 32) >> 4), ID2B, ks > 0, go);
     mma_commit_pred(x.bar(B_V_EMPTY + s), go);
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
       mma_ts_tf32_pred(tWO0 + 32, tU0 + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
-    mma_commit_pred(x.bar(B_O_FULL + ob0), go);
-    if (dual) {
+    mma_commit_pred(x.bar(B_O_FULL + 0), go);
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++)
-        mma_ts_tf32_pred(tWO1 + 32, tU1 + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
-      mma_commit_pred(x.bar(B_O_FULL + 1), go);
-    }
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tWO1 + 32, tU1 + 8 * ks, d_m + so + (uint64_t)((ks * 32) >> 4), ID3B, 1, go);
+    mma_commit_pred(x.bar(B_O_FULL + 1), go);
     x.wait(B_S_READY, (uint32_t)((c + 1) & 1), E_MMA, 0);
     tc_fence_after();
 #pragma unroll
     for (int ks = 0; ks < 4; ks++)
       mma_ts_tf32_pred(tS0, tU0 + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
-    if (dual) {
-      x.wait(B_S_READY_T, (uint32_t)((c + 1) & 1), E_MMA, 0);
-      tc_fence_after();
+    x.wait(B_S_READY_T, (uint32_t)((c + 1) & 1), E_MMA, 0);
+    tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++)
-        mma_ts_tf32_pred(tS1, tU1 + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
-    }
+    for (int ks = 0; ks < 4; ks++)
+      mma_ts_tf32_pred(tS1, tU1 + 8 * ks, d_kr + so + (uint64_t)((ks * 4096) >> 4), ID3A, 1, go);
     mma_commit_pred(x.bar(B_CONS_EMPTY + s), go);
   }
   mma_commit_pred(x.bar(B_MMA1_DONE), go);         // the final states are complete
-  if (dual) mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
+  mma_commit_pred(x.bar(B_MMA1_DONE_T), go);
   mma_commit_pred(x.bar(B_DRAIN), go);
   if (!mbar_wait_drain(x.bar(B_DRAIN), 0, x.abort_flag)) atomicCAS(const_cast<int*>(x.abort_flag), 0, E_DRAIN + B_DRAIN);
 }
@@ -1093,13 +961,13 @@ __device__ __forceinline__ void decay64(uint32_t tS, const float* dcol) {
 }
 
 template <int KF>
-__device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int hf, int lane, bool dual) {
+__device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx& x, uint32_t tmem, int quarter, int hf, int lane) {
   const int v = 32 * quarter + lane;
   const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
   const uint32_t tS0 = tmem + TD_S0 + lane_base + 64 * hf, tS1 = tmem + TD_S1 + lane_base + 64 * hf;
   // ---- initial states -> tensor memory: chain L as the task says, chain Tr the identity
 #pragma unroll 1
-  for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+  for (int ch = 0; ch < 2; ch++) {
 #pragma unroll 1
     for (int j = 0; j < 2; j++) {
       const int col0 = 64 * hf + 32 * j;
@@ -1137,7 +1005,7 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
     const bool last = c == x.nchunks;
     const float* dcol = reinterpret_cast<const float*>(x.smem + OFF_DEC) + (c & 3) * D + 64 * hf;
 #pragma unroll 1
-    for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
+    for (int ch = 0; ch < 2; ch++) {
       x.wait(ch ? B_MMA1_DONE_T : B_MMA1_DONE, (uint32_t)(c & 1), E_SCALE);
       tc_fence_after();
       const uint32_t tS = ch ? tS1 : tS0;
@@ -1160,16 +1028,15 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
     // ---- output rows of this chunk, chain L then chain Tr
     const int nvalid = min(C, x.len - c * C);
 #pragma unroll 1
-    for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
-      const int ob = dual ? ch : (c & 1);                  // see role_mma_dual
-      x.wait(B_O_FULL + ob, (uint32_t)(dual ? (c & 1) : ((c >> 1) & 1)), E_EPI);
+    for (int ch = 0; ch < 2; ch++) {
+      x.wait(B_O_FULL + ch, (uint32_t)(c & 1), E_EPI);       // one output buffer per chain (see role_mma_dual)
       tc_fence_after();
       uint32_t o[16];
-      tmem_ld16(tmem + (dual ? (ch ? TD_WO1 : TD_WO0) : TM_WO + 64 * (c & 1)) + 32 + 16 * hf + lane_base, o);
+      tmem_ld16(tmem + (ch ? TD_WO1 : TD_WO0) + 32 + 16 * hf + lane_base, o);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + ob));
+      if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + ch));
       if (!(task.flags & TF_NO_OUT)) {
         __nv_bfloat16* orow = (ch ? obase1 : obase0) + (x.t0 + (long long)c * C + 16 * hf) * p.ldo;
 #pragma unroll
@@ -1180,14 +1047,23 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
   }
 }
 
+// ------------------------------------------------------------------------------------------------ kernel
 template <int FE, int KF>
-__global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
+__global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkParams p, const __grid_constant__ TmaMaps maps) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = tid >> 5;
   const int H = p.H;
   const int rank = blockIdx.x / H, h = blockIdx.x % H;
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");     // chained behind the task planner (see the kernel above)
+
+  // Launched as a programmatic dependent of the planner (its CTAs become resident while the planner still runs): wait
+  // here until the planner's writes (status, task table) are visible.  A no-op for an ordinary launch.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  if (p.status[0] & 1) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
+    const long long rows = p.T * H;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x)
+      if (tid < 16) reinterpret_cast<uint4*>(p.out + (r / H) * p.ldo + (r % H) * D)[tid] = make_uint4(0, 0, 0, 0);
+  }
   if (rank >= *p.n_tasks) return;
   const Task task = p.tasks[rank];
   Ctx x;
@@ -1202,9 +1078,11 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
   x.prof = p.prof;
   const long long prof_t0 = clock64();
 #endif
-  const bool dual = (task.flags & TF_DUAL) != 0;
+
+  const bool dual = (task.flags & TF_DUAL) != 0;   // both chains of a mapped segment in this task (see the dual-chain roles)
   if (x.nchunks == 0) {
-    // empty run: chain L passes its state through, the transition map of no tokens is the identity
+    // empty run: the state passes through (source -> destination) without touching tensor memory; the transition map
+    // of no tokens is the identity
     for (int ch = 0; ch < (dual ? 2 : 1); ch++) {
       float* dst = ch ? task.dst2 : task.dst;
       if (dst == nullptr) continue;
@@ -1224,6 +1102,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
     }
     return;
   }
+
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile int* range_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 12);
   if (tid == 0) {
@@ -1235,7 +1114,8 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
       mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
       mbar_init(x.bar(B_QK_FULL + i), 1);
       mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
-      mbar_init(x.bar(B_V_FULL + i), 1);
+      // diagnostic switch: the v barriers expect one arrival more than they will ever get, so their waiters give up
+      mbar_init(x.bar(B_V_FULL + i), (p.debug_flags & DBG_STALL_V_STREAM) ? 2 : 1);
       mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
       mbar_init(x.bar(B_CONS_EMPTY + i), 1);
       mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
@@ -1243,7 +1123,7 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
       mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
       mbar_init(x.bar(B_V_EMPTY + i), 1);
       mbar_init(x.bar(B_L_EMPTY + i), 1);
-      mbar_init(x.bar(B_O_FULL + i), 1);       // here: one per chain
+      mbar_init(x.bar(B_O_FULL + i), 1);
       mbar_init(x.bar(B_O_EMPTY + i), 8);
     }
     mbar_init(x.bar(B_MMA1_DONE), 1);
@@ -1265,7 +1145,8 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
   const bool v_zero = (task.flags & TF_V_ZERO) != 0;
 
   if (warp == W_MMA) {
-    role_mma_dual(x, tmem, v_zero, dual);
+    if (dual) role_mma_dual(x, tmem, v_zero);
+    else role_mma(x, tmem, v_zero);
     __syncwarp();
   } else if (warp == W_INV0 || warp == W_INV0 + 1) {
     role_inverse(x, warp - W_INV0, lane);
@@ -1273,11 +1154,13 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_dual_kernel(const ChunkP
     role_loader<FE>(p, maps, x, lane);
     __syncwarp();
   } else if (warp < W_PREP0) {
-    role_tmem_dual<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane, dual);
+    if (dual) role_tmem_dual<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
+    else role_tmem<KF>(p, task, x, tmem, warp & 3, (warp - W_SCALE0) >> 2, lane);
   } else {
     const int pt = tid - W_PREP0 * 32;
     role_prep<FE>(p, x, pt / PREP_THREADS, pt % PREP_THREADS);
   }
+
 #ifdef KDA_PROF
   if (lane == 0 && blockIdx.x == 0 && x.prof != nullptr) {
     const int role = warp == W_MMA ? 4 : (warp <= 2 ? 3 : (warp == W_LOAD ? 1 : (warp < W_PREP0 ? 5 : 2)));
@@ -1316,35 +1199,6 @@ cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_t
   if (blocks <= 0) return cudaSuccess;
   // Chained behind the planner by programmatic dependent launch when it directly follows it in the stream (function
   // of kda/b200/csrc/w3/base/cake/launch_m128.cu:37-60): the launch latency hides under the planner.
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(u::THREADS);
-  cfg.dynamicSmemBytes = u::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = after_planner ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kerns[p.frontend ? 1 : 0][p.key_first ? 1 : 0], p, maps);
-}
-
-cudaError_t launch_chunk_dual(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner) {
-  typedef void (*Kern)(const ChunkParams, const TmaMaps);
-  static const Kern kerns[2][2] = {{u::kda_chunk_dual_kernel<0, 0>, u::kda_chunk_dual_kernel<0, 1>},
-                                   {u::kda_chunk_dual_kernel<1, 0>, u::kda_chunk_dual_kernel<1, 1>}};
-  static int attr_dev_mask = 0;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!(attr_dev_mask & (1 << (dev & 31)))) {
-    for (int i = 0; i < 4; i++) {
-      cudaError_t e = cudaFuncSetAttribute(kerns[i >> 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize, u::SMEM_BYTES);
-      if (e != cudaSuccess) return e;
-    }
-    attr_dev_mask |= 1 << (dev & 31);
-  }
-  const long long blocks = (long long)n_task_cap * p.H;
-  if (blocks <= 0) return cudaSuccess;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
   cfg.blockDim = dim3(u::THREADS);

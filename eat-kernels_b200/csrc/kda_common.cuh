@@ -18,7 +18,7 @@ constexpr uint32_t TF_INIT_IDENTITY = 2u;  // start from S = I (transition chain
 constexpr uint32_t TF_V_ZERO = 4u;         // treat v as 0 (transition chain)
 constexpr uint32_t TF_OUT_AUX = 8u;        // write output rows to the auxiliary tensor (Qt)
 constexpr uint32_t TF_NO_OUT = 16u;        // do not write output rows
-constexpr uint32_t TF_DUAL = 64u;          // dual-chain kernel only: run chain L (this task's own flags, real v -> out, dst) AND
+constexpr uint32_t TF_DUAL = 64u;          // tcgen05 kernel only: run chain L (this task's own flags, real v -> out, dst) AND
                                            // chain Tr (S = I, v = 0 -> out_aux, dst2) over one operand preparation
 constexpr uint32_t TF_DST_VF = 32u;        // store the final state value-first whatever the launch's state layout
                                            // (transition maps: the scan applies them as  E <- E P)

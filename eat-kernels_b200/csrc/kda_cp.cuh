@@ -12,7 +12,7 @@ struct SegPlanParams {
   const int* need_map;
   const float* src_base; long long src_stride;
   int no_out;      // maps only: neither chain writes output rows
-  int dual;        // 1: a mapped segment is ONE dual-chain task (tcgen05 dual kernel); 0: two tasks, chains L and Tr
+  int dual;        // 1: a mapped segment is ONE dual-chain task (tcgen05 kernel only); 0: two tasks, chains L and Tr
   float* P;
   float* S_loc;
   Task* tasks;     // [2 * n_seg] (dual: n_seg used)

@@ -25,6 +25,12 @@ constexpr int CUT_MAX_SEQS = 1024;       // sequences a cut plan is made for (be
 constexpr int N_CAND = 9;                // candidate piece lengths
 constexpr int MIN_PIECE_CHUNKS = 16;     // shorter pieces drown in the per-task cost
 constexpr int TASK_OVERHEAD = 3;         // start / end of a task, in chunk steps
+constexpr int DUAL_X8 = 13;              // a dual-chain chunk step costs 13 / 8 single-chain ones (measured 1.62)
+
+// chunk steps of the map of one piece of lp chunks: one dual-chain task, or two single-chain tasks
+__device__ __forceinline__ long long map_task_cost(int lp, int dual) {
+  return dual ? (long long)(DUAL_X8 * lp + 7) / 8 + TASK_OVERHEAD : 2LL * (lp + TASK_OVERHEAD);
+}
 constexpr int SCAN_STEPS_X16 = 12;       // one map of the scan chain, in 1/16 chunk steps
 constexpr int LAUNCH_STEPS = 4;          // the scan launch and the second kernel launch, in chunk steps
 __host__ __device__ constexpr int cand_pieces(int k) { return k < 3 ? k + 2 : (k == 3 ? 6 : (k == 4 ? 8 : (k == 5 ? 12 : (k == 6 ? 16 : (k == 7 ? 24 : 32))))); }
@@ -229,7 +235,8 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
     if (tid == 0) {
       // Times in chunk steps.  A launch cannot end before its longest task, nor before its share of the work, nor before
       // the SM that gets the most piece-sized tasks has run them all (pieces are equal, so few of them come in waves).
-      // A cut sequence of p pieces puts 2 p - 3 piece-sized tasks into the first launch and p - 1 into the second; the
+      // A cut sequence of p pieces puts piece 0 and the maps of pieces 1 .. p-2 into the first launch (a map is one
+      // dual-chain task of DUAL_X8 / 8 chunk steps per chunk, or two plain tasks) and p - 1 pieces into the second; the
       // uncut sequences are spread over both launches so that both carry about the same work.
       const long long Hh = a.H, nsm = a.n_sm;
       long long best = max(((long long)s_uncut_work * Hh + nsm - 1) / nsm, (long long)(cmax + TASK_OVERHEAD));
@@ -238,11 +245,15 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
         const int lp = lp_of[k];
         if (lp == 0 || s_ncut[k] == 0 || s_pieces[k] > a.max_pieces) continue;
         const long long pt = lp + TASK_OVERHEAD;
-        const long long ka = 2LL * s_pieces[k] - 3LL * s_ncut[k], kb = (long long)s_pieces[k] - s_ncut[k];
+        const long long nmap = (long long)s_pieces[k] - 2LL * s_ncut[k];             // mapped pieces
+        const long long ka = a.dual ? s_ncut[k] + nmap : s_ncut[k] + 2 * nmap;       // tasks of the first launch
+        const long long kb = (long long)s_pieces[k] - s_ncut[k];
+        const long long wcut = a.dual ? pt * s_ncut[k] + map_task_cost(lp, 1) * nmap : pt * ka;
+        const long long pa = wcut / max(1LL, ka);                                    // mean task of the first launch
         const long long U = s_work[k];
-        const long long to_b = max(0LL, min(U, (pt * (ka + kb) + U) / 2 - pt * kb));
-        const long long wa = pt * ka + U - to_b, wb = pt * kb + to_b;
-        const long long ta = max(max((wa * Hh + nsm - 1) / nsm, ((ka * Hh + nsm - 1) / nsm) * pt), (long long)max(s_longest[k], lp) + TASK_OVERHEAD);
+        const long long to_b = max(0LL, min(U, (wcut + pt * kb + U) / 2 - pt * kb));
+        const long long wa = wcut + U - to_b, wb = pt * kb + to_b;
+        const long long ta = max(max((wa * Hh + nsm - 1) / nsm, ((ka * Hh + nsm - 1) / nsm) * pa), (long long)max(s_longest[k], lp) + TASK_OVERHEAD);
         const long long tb = max(max((wb * Hh + nsm - 1) / nsm, ((kb * Hh + nsm - 1) / nsm) * pt), pt);
         const long long t = ta + tb + (SCAN_STEPS_X16 * (long long)(cand_pieces(k) - 2) + 15) / 16 + LAUNCH_STEPS;
         if (t * 10 < best * 9) { best = t; best_lp = lp; }          // cut only for a clear gain
@@ -273,7 +284,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
         if (c <= lp + lp / 4) uncut += c > 0 ? c + TASK_OVERHEAD : 0;
         else {
           const int p = (c + lp - 1) / lp;
-          wa += (long long)(lp + TASK_OVERHEAD) * (2 * p - 3);
+          wa += (lp + TASK_OVERHEAD) + (long long)map_task_cost(lp, a.dual) * (p - 2);
           wb += (long long)(lp + TASK_OVERHEAD) * (p - 1);
         }
       }
@@ -309,7 +320,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
           if (to_b) cb = 1; else ca = 1;
         } else {
           const int p = (c + lp - 1) / lp;
-          ca = (unsigned char)(2 * p - 3);
+          ca = (unsigned char)(a.dual ? p - 1 : 2 * p - 3);
           cb = (unsigned char)(p - 1);
           nm += p - 1;
           nc += 1;
@@ -359,10 +370,16 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
           Task l;
           l.t0 = t0; l.len = len; l.flags = TF_INIT_ZERO | TF_NO_OUT; l.src = nullptr; l.ck = nullptr; l.dst2 = nullptr;
           l.dst = a.map_L + (size_t)(m0 + q) * slot_elems;
-          a.tasks[ia++] = l;
-          l.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_NO_OUT | TF_DST_VF;
-          l.dst = a.map_P + (size_t)(m0 + q) * slot_elems;
-          a.tasks[ia++] = l;
+          if (a.dual) {                                 // both chains in one task
+            l.flags |= TF_DUAL;
+            l.dst2 = a.map_P + (size_t)(m0 + q) * slot_elems;
+            a.tasks[ia++] = l;
+          } else {
+            a.tasks[ia++] = l;
+            l.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_NO_OUT | TF_DST_VF;
+            l.dst = a.map_P + (size_t)(m0 + q) * slot_elems;
+            a.tasks[ia++] = l;
+          }
         }
         Task r;                                         // the piece itself, from its entering state
         r.t0 = t0; r.len = len; r.flags = 0; r.dst2 = nullptr;

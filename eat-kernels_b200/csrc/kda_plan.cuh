@@ -35,6 +35,7 @@ struct PlanParams {
   int max_pieces;           // capacity: pieces of all cut sequences together (0 = never cut)
   int n_sm;                 // SMs of the device (cost model)
   int key_first;            // state layout of the launch (the transition maps are stored value-first either way)
+  int dual;                 // 1: the map of a piece is one dual-chain task (tcgen05 kernel); 0: two single-chain tasks
   Task* tasks_b;            // second launch: [2 * max_pieces] (pieces, and up to max_pieces uncut sequences for balance)
   int* n_tasks_b;
   float* map_P;             // [max_pieces][H][128][128] transition maps
@@ -49,9 +50,7 @@ cudaError_t launch_plan(const PlanParams& a, cudaStream_t stream);
 cudaError_t launch_scan_chains(const ScanChain* chains, const int* n_chains, int max_chains, const float* P, const float* L, float* E,
                                int H, int key_first, cudaStream_t stream);
 cudaError_t launch_chunk_fwd(const ChunkParams& p, int n_task_cap, cudaStream_t stream);    // mma.sync kernel
-// tcgen05 dual-chain kernel: tasks with TF_DUAL run chain L and the transition chain over one operand preparation
-cudaError_t launch_chunk_dual(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner = false);
-// tcgen05 kernel; after_planner: the launch directly follows launch_plan / launch_seg_plan in the stream and is chained
+// tcgen05 kernel (tasks with TF_DUAL run chain L and the transition chain over one operand preparation); after_planner: the launch directly follows launch_plan / launch_seg_plan in the stream and is chained
 // to it by programmatic dependent launch
 cudaError_t launch_chunk_umma(const ChunkParams& p, const TmaMaps& maps, int n_task_cap, cudaStream_t stream, bool after_planner = false);
 

@@ -11,7 +11,7 @@ LIB_PATH = PKG / "libkda_b200.so"
 FRONTEND_RAW, FRONTEND_PLAIN = 0, 1
 STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
 NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
-KERNEL_TCGEN05, KERNEL_MMA_SYNC, KERNEL_TCGEN05_DUAL = 0, 1, 2
+KERNEL_TCGEN05, KERNEL_MMA_SYNC, KERNEL_TCGEN05_TWO_TASK = 0, 1, 2
 MAX_CUT_PIECES = 128
 EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_workspace_bytes_cuts", "kda_prefill_launch", "kda_prefill_plan_counts", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
            "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",

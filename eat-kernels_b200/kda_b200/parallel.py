@@ -92,11 +92,12 @@ DUAL_COST = 1.62     # a dual-chain chunk step in units of a single-chain one (m
 @functools.lru_cache(maxsize=256)        # the search costs milliseconds on the host; layouts repeat call after call
 def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_steps_per_chunk_head=0.0025):
     """Piece boundaries (chunk-aligned token offsets, first 0, last T) of one rank's shard, chosen by simulating the
-    segment launch: on the first rank every mapped piece is two tasks per head (chains L and Tr) and the first piece one
-    plain task per head; on the other ranks every piece is mapped and is ONE dual-chain task per head (`DUAL_COST`); a task costs its chunks plus `task_overhead` chunk steps, and mapped tokens cost a fix-up pass.
-    On the first rank the plain first piece may be LONGER than the mapped pieces: while its H CTAs run, the remaining
-    SMs work through the doubled chains of the shorter pieces (with H = 96 on 148 SMs the plain chain alone would
-    leave a third of the GPU idle)."""
+    segment launch: the first piece of the first rank is one plain task per head, every mapped piece ONE dual-chain task
+    per head (`DUAL_COST`; with `CudaBackend(dual=False)` or the cross-check kernel it is two plain tasks, which this
+    model does not follow); a task costs its chunks plus `task_overhead` chunk steps, and mapped tokens cost a fix-up
+    pass.  On the first rank the plain first piece may be LONGER than the mapped pieces: while its H CTAs run, the
+    remaining SMs work through the dual chains of the shorter pieces (with H = 96 on 148 SMs the plain chain alone
+    would leave a third of the GPU idle)."""
     nch = -(-T // CHUNK)
     if nch <= 1:
         return [0, T], (float(nch) + task_overhead, 0.0)
@@ -111,9 +112,8 @@ def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_st
             pieces = [base + (1 if i < extra else 0) for i in range(m)]
             costs = [c_first + task_overhead] * H if c_first else []
             for c in pieces:
-                # first rank: the plain first piece keeps the launch on the single-chain kernel, a mapped piece is two
-                # tasks per head; other ranks: every piece is mapped and runs as one dual-chain task per head
-                costs += [c + task_overhead] * (2 * H) if first_rank else [DUAL_COST * c + task_overhead] * H
+                # a mapped piece runs as one dual-chain task per head
+                costs += [DUAL_COST * c + task_overhead] * H
             seg = _makespan(costs, n_sms)
             fix = fixup_steps_per_chunk_head * rest * H
             if best_cost is None or seg + fix < sum(best_cost) - 1e-9:
@@ -184,7 +184,7 @@ class CudaBackend:
         from . import default_kernel
         self.lib = _cabi.lib()
         self.kernel = default_kernel() if kernel is None else int(kernel)
-        self.dual = bool(dual)      # all-mapped segment launches run on the dual-chain kernel (False: two tasks per segment)
+        self.dual = bool(dual)      # a mapped segment is one dual-chain task (False: two tasks, chains L and Tr)
         # reuse=True: every result and scratch tensor is allocated once per shape and handed out again at the next call
         # (a serving loop over one layout then allocates nothing after its first step; results of a call are only
         # valid until the next one)
@@ -225,8 +225,10 @@ class CudaBackend:
         return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
     def segment_maps(self, q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first_state):
-        """Runs chain L (and chain Tr where need_map) for the pieces [bounds[i], bounds[i+1]).
-        Returns out [1,T,H,128] bf16 (o_loc), qt [1,T,H,128] bf16, P, S_loc [n,H,128,128] fp32 (value-first)."""
+        """Runs chain L (and chain Tr where need_map) for the pieces [bounds[i], bounds[i+1]) in one launch.
+        Returns out [1,T,H,128] bf16 (o_loc), qt [1,T,H,128] bf16, P, S_loc [n,H,128,128] fp32 (value-first).
+        On the tcgen05 kernel a mapped piece is ONE dual-chain task per head (both chains over one operand
+        preparation) next to the plain tasks of unmapped pieces; `dual=False` keeps the two-task scheme."""
         dev = q.device
         T, H = q.shape[1], q.shape[2]
         n = len(bounds) - 1
@@ -256,8 +258,7 @@ class CudaBackend:
             a.src_base, a.src_slot_stride, a.src_slots = first_state.data_ptr(), first_state.stride(0), first_state.shape[0]
         a.workspace, a.workspace_bytes = (ws.data_ptr() + 255) // 256 * 256, ws_bytes
         a.status = status.data_ptr()
-        # all segments mapped (every rank but the first): one dual-chain task per segment and head
-        a.kernel = _cabi.KERNEL_TCGEN05_DUAL if (self.dual and self.kernel == _cabi.KERNEL_TCGEN05 and all(need_map)) else self.kernel
+        a.kernel = _cabi.KERNEL_TCGEN05_TWO_TASK if (self.kernel == _cabi.KERNEL_TCGEN05 and not self.dual) else self.kernel
         s.n_seg = n
         s.seg_t0, s.seg_t1, s.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
         s.qt, s.P, s.S_loc = qt.data_ptr(), P.data_ptr(), S_loc.data_ptr()

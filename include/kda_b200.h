@@ -53,11 +53,12 @@ enum {
   KDA_KERNEL_TCGEN05 = 0,  /* tcgen05 / tensor-memory kernel (default) */
   KDA_KERNEL_MMA_SYNC = 1, /* warp-level mma.sync kernel: same results within tolerance, kept as an independent
                               cross-check of the tensor-memory path */
-  KDA_KERNEL_TCGEN05_DUAL = 2  /* kda_segment_launch only (elsewhere the same as KDA_KERNEL_TCGEN05): a mapped segment
-                              runs as ONE task of the dual-chain tcgen05 kernel, both chains over one operand
-                              preparation (kda/b200/csrc/w3/base/cake_dual/kda_m128.cu:821-823); about 12 % cheaper
-                              than two single-chain tasks, while an unmapped segment costs a third more in that
-                              kernel: meant for calls whose segments are all mapped */
+  KDA_KERNEL_TCGEN05_TWO_TASK = 2  /* kda_segment_launch only (elsewhere the same as KDA_KERNEL_TCGEN05): chains L and
+                              Tr of a mapped segment as two single-chain tasks.  With KDA_KERNEL_TCGEN05 a mapped
+                              segment is ONE dual-chain task, both chains over one operand preparation
+                              (kda/b200/csrc/w3/base/cake_dual/kda_m128.cu:821-823): bit-identical results, about
+                              1.6 instead of 2 chunk steps per chunk; this value keeps the two-task scheme
+                              available as the cross-check */
 };
 
 /* Bits of status[0] (table validation, same meaning as kda/b200/kda_b200.py:56-62). */

@@ -42,12 +42,14 @@ def test_context_parallel_single_gpu(kda, H, T, pieces, slow, kernel):
     ko.check_close(fin.cpu(), f2.cpu(), tag + " vs plain call (state)", 6e-3)
 
 
-@pytest.mark.parametrize("H,bounds,slow", [(4, [0, 500, 1000], False), (2, [0, 33, 64, 1000, 2047], True), (148, [0, 4096], False),
-                                           (3, [0, 1, 40], False)])
-def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow):
-    """A mapped segment as ONE task of the dual-chain kernel (both chains over one operand preparation) gives the
-    outputs, Qt rows and state maps of the two-task scheme (chain L and chain Tr as separate tasks): the same products
-    in the same order, so bit for bit; and the maps reproduce the plain chain's final state."""
+@pytest.mark.parametrize("H,bounds,slow,plain_first", [(4, [0, 500, 1000], False, False), (2, [0, 33, 64, 1000, 2047], True, False),
+                                                       (148, [0, 4096], False, False), (3, [0, 1, 40], False, False),
+                                                       (5, [0, 640, 900, 1500], False, True), (150, [0, 2048, 2560], True, True)])
+def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow, plain_first):
+    """A mapped segment as ONE dual-chain task (both chains over one operand preparation) gives the outputs, Qt rows and
+    state maps of the two-task scheme (chain L and chain Tr as separate tasks): the same products in the same order, so
+    bit for bit; and the maps reproduce the plain chain's final state.  `plain_first`: the launch mixes a plain first
+    piece (from the caller's state) with dual-chain tasks, as the first rank of a context-parallel call does."""
     from kda_b200 import parallel
     T = bounds[-1]
     inputs = ko.make_inputs_raw(H, [T], 50 + H)
@@ -55,12 +57,19 @@ def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow):
         slow_gates_(inputs, 50)
     q, k, v, g, beta, A_log, dt_bias, scale, init, _ = to_dev(inputs)
     need = [1] * (len(bounds) - 1)
+    if plain_first:
+        need[0] = 0
     res = {}
     for dual in (True, False):
         be = parallel.CudaBackend(dual=dual)
-        res[dual] = [t.clone() for t in be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need, None)]
+        res[dual] = [t.clone() for t in be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need,
+                                                        init if plain_first else None)]
         torch.cuda.synchronize()
+        assert be.kernel_error() == 0
+    t_map = bounds[1] if plain_first else 0          # Qt rows exist for mapped tokens only
     for name, a, b in zip(("o_loc", "Qt", "P", "S_loc"), res[True], res[False]):
+        if name == "Qt":
+            a, b = a[:, t_map:], b[:, t_map:]
         assert torch.equal(a, b), f"dual-chain {name} differs from the two-task scheme (H={H}, bounds={bounds})"
     # compose the maps from the initial state and compare with the plain call's final state
     S = init[0].double().cpu()
