@@ -565,6 +565,9 @@ def main(argv=None):
     launch = kda_b200.prepare_plain(q, k, v, g, beta, D ** -0.5, pool, False, cu, dynamic_layout=True,
                                     ssm_state_indices=slots, state_checkpoints=ck, checkpoint_cu_starts=ck_starts,
                                     checkpoint_every_n_tokens=CK_EVERY)
+    # kernels of this library per step: planner + chunk kernel, and with cut capacity the scan of cut chains + the
+    # chunk kernel's second launch (both run every step; they find no work when the planner cuts nothing)
+    launches_per_step = 4 if launch._args.max_cut_pieces > 0 else 2
 
     def barrier():
         if world > 1:
@@ -724,7 +727,7 @@ def main(argv=None):
                        "flops_per_launch": flops,
                        "note": "dense count 163840 FLOP per token-head (chunk 64 convention); `peak` is the sustained "
                                "bf16 figure, `peak_burst` the burst one: the timed region lies between the two definitions"},
-            "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         }
         if verified is not None:
             line.update(verified=True, verification=verified)
