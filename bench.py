@@ -514,6 +514,8 @@ def main(argv=None):
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle verification before timing (profiler captures)")
     ap.add_argument("--no-longctx", action="store_true", help="N > 1: skip the context-parallel configs[3] measurement")
     ap.add_argument("--small", action="store_true", help="8 requests, for profiler captures (not a bench value)")
+    ap.add_argument("--shard-of", type=int, default=1, help="one GPU runs the head shard that each of N GPUs would run "
+                    "(tuning the few-heads case without N GPUs; not a bench value)")
     ap.add_argument("--workload", default="serving", choices=["serving", "longctx", "layouts", "headline"],
                     help="serving = configs[2] (the default, head-parallel); longctx = configs[3], one 131072-token "
                          "sequence at H=96, context-parallel over the ranks")
@@ -550,8 +552,8 @@ def main(argv=None):
         if world > 1:
             raise SystemExit("--workload layouts runs on one GPU")
         return run_layouts(args, dev, kda_b200)
-    assert H_TOTAL % world == 0
-    H = H_TOTAL // world
+    assert H_TOTAL % (world * args.shard_of) == 0
+    H = H_TOTAL // (world * args.shard_of)
     T, N = sum(lens), len(lens)
     q, k, v, g, beta = make_device_inputs(H, lens, 100 + rank, dev)
     gen = torch.Generator(device=dev).manual_seed(7)
@@ -717,6 +719,7 @@ def main(argv=None):
                                    "lengths lognormal(ln1024,0.8) clipped [16,8192], fp32 pool of 256 slots, bf16 checkpoints "
                                    "every 1024 tokens, pre-activated bf16 q/k/v + fp32 g/beta" + (" [--small]" if args.small else ""),
                        "tokens": T, "requests": N, "heads_per_gpu": H, "checkpoint_rows": rows,
+                       "planner": dict(zip(("tasks_first_launch", "tasks_second_launch", "cut_sequences"), launch.plan_counts())),
                        "l2": "inputs (GBs per step) far exceed L2; no flush needed", "parallelism": f"hp{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],

@@ -209,6 +209,7 @@ int kda_prefill_launch(const KdaPrefillArgs* a, void* stream_) {
   pl.n_tasks = w.n_tasks; pl.status = a->status;
   pl.max_pieces = pieces; pl.n_sm = sm_count(); pl.key_first = a->state_layout == KDA_STATE_KEY_FIRST;
   pl.dual = a->kernel != KDA_KERNEL_MMA_SYNC;
+  pl.force_cand = (g_debug_flags & kda::DBG_FORCE_CAND_MASK) >> kda::DBG_FORCE_CAND_SHIFT;
   if (pieces > 0) {
     pl.tasks_b = w.tasks_b; pl.n_tasks_b = w.n_tasks + 1; pl.n_chains = w.n_tasks + 2; pl.chains = w.chains;
     pl.map_P = w.map_P; pl.map_L = w.map_L; pl.map_E = w.map_E;
@@ -384,7 +385,7 @@ int kda_prefill_plan_counts(const KdaPrefillArgs* a, int32_t* counts, void* stre
 }
 
 int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters) {
-  if (wait_limit_us < 0 || (flags & ~kda::DBG_STALL_V_STREAM)) return KDA_ERR_ARG;
+  if (wait_limit_us < 0 || (flags & ~(kda::DBG_STALL_V_STREAM | kda::DBG_FORCE_CAND_MASK))) return KDA_ERR_ARG;
   g_wait_limit_ns = (unsigned long long)wait_limit_us * 1000ull;
   g_debug_flags = flags;
   g_prof = reinterpret_cast<unsigned long long*>(prof_counters);

@@ -63,6 +63,8 @@ struct ChunkParams {
 
 // Diagnostic switches of the tcgen05 kernel (set only through kda_debug_configure).
 constexpr int DBG_STALL_V_STREAM = 1;  // the v tiles never count as arrived: their waiters run into the bound
+// bits 8-11: k + 1 makes the device planner take candidate k of its piece lengths (a tuning aid for the cost model)
+constexpr int DBG_FORCE_CAND_SHIFT = 8, DBG_FORCE_CAND_MASK = 0xf00;
 
 // ----------------------------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -258,6 +258,10 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
         const long long t = ta + tb + (SCAN_STEPS_X16 * (long long)(cand_pieces(k) - 2) + 15) / 16 + LAUNCH_STEPS;
         if (t * 10 < best * 9) { best = t; best_lp = lp; }          // cut only for a clear gain
       }
+      if (a.force_cand > 0 && a.force_cand <= N_CAND) {
+        const int k = a.force_cand - 1;
+        if (lp_of[k] != 0 && s_ncut[k] != 0 && s_pieces[k] <= a.max_pieces) best_lp = lp_of[k];
+      }
       s_lp = best_lp;
     }
   }

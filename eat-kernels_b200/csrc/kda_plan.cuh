@@ -36,6 +36,7 @@ struct PlanParams {
   int n_sm;                 // SMs of the device (cost model)
   int key_first;            // state layout of the launch (the transition maps are stored value-first either way)
   int dual;                 // 1: the map of a piece is one dual-chain task (tcgen05 kernel); 0: two single-chain tasks
+  int force_cand;           // tuning aid: k + 1 forces candidate k of the piece lengths (if it is valid), 0 = cost model
   Task* tasks_b;            // second launch: [2 * max_pieces] (pieces, and up to max_pieces uncut sequences for balance)
   int* n_tasks_b;
   float* map_P;             // [max_pieces][H][128][128] transition maps

@@ -398,11 +398,12 @@ def prepare_cut_sequence(q, k, v, g, beta, A_log, dt_bias, scale, pool, slot, *,
     return launch
 
 
-def compose_rank_map(backend, P, S_loc):
-    """Total map of a rank's pieces per head: P_rank = P_0 @ P_1 @ ..., L_rank = (..(S_loc_0 @ P_1 + S_loc_1) @ P_2 ..)."""
+def compose_rank_map(backend, P, S_loc, first_is_zero=False):
+    """Total map of a rank's pieces per head: P_rank = P_0 @ P_1 @ ..., L_rank = (..(S_loc_0 @ P_1 + S_loc_1) @ P_2 ..).
+    `first_is_zero`: P_0 is the zero map (a plain first piece, which starts from a known state), so is the product."""
     n = P.shape[0]
     _, L_rank = backend.scan(P, S_loc, None)
-    if n == 1:
+    if n == 1 or first_is_zero:
         return P[0], L_rank
     zeros = backend._buf("zeros", tuple(S_loc[1:].shape), torch.float32, P.device, zero=True) if hasattr(backend, "_buf") \
         else torch.zeros_like(S_loc[1:])
@@ -456,7 +457,7 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
         out = backend.fixup(out, qt, S_in, bounds, need_map)
         mark("fixup")
         return out, S_final[None]
-    P_rank, L_rank = compose_rank_map(backend, P, S_loc)
+    P_rank, L_rank = compose_rank_map(backend, P, S_loc, first_is_zero=not need_map[0])
     mark("maps")
     if world > 1:
         # two gathers straight into the layout the scan reads ([rank][H][128][128] each): no stacking, no copies

@@ -221,6 +221,8 @@ const char* kda_version(void);
  *                  memory and writes a code to status[2].
  *   flags          bit 0: the arrival of the v tiles is never signalled to their consumers, so that a waiter runs into
  *                  the bound (used to test the give-up path without faulting or hanging anything); 0 = normal.
+ *                  bits 8-11: k + 1 makes the device planner cut with candidate k of its piece lengths (the longest
+ *                  sequence in 2, 3, 4, 6, 8, 12, 16, 24, 32 pieces) instead of asking its cost model (tuning aid).
  *   prof_counters  device uint64[1024] receiving per-role cycle counters in builds compiled with -DKDA_PROF; NULL else. */
 int kda_debug_configure(int64_t wait_limit_us, int32_t flags, void* prof_counters);
 
