@@ -694,6 +694,7 @@ def main(argv=None):
 
     # ---- N > 1: the context-parallel configuration (configs[3]) as well, after the headline timing, so that one
     # launch per N yields both scaling curves.  The serving tensors are released first.
+    planner_counts = dict(zip(("tasks_first_launch", "tasks_second_launch", "cut_sequences"), launch.plan_counts()))
     longctx = None
     if world > 1 and not args.no_longctx and not args.small:
         del launch, q, k, v, g, beta, pool, ck
@@ -719,7 +720,7 @@ def main(argv=None):
                                    "lengths lognormal(ln1024,0.8) clipped [16,8192], fp32 pool of 256 slots, bf16 checkpoints "
                                    "every 1024 tokens, pre-activated bf16 q/k/v + fp32 g/beta" + (" [--small]" if args.small else ""),
                        "tokens": T, "requests": N, "heads_per_gpu": H, "checkpoint_rows": rows,
-                       "planner": dict(zip(("tasks_first_launch", "tasks_second_launch", "cut_sequences"), launch.plan_counts())),
+                       "planner": planner_counts,
                        "l2": "inputs (GBs per step) far exceed L2; no flush needed", "parallelism": f"hp{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["src"],

@@ -307,7 +307,12 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   sp.need_map = s->seg_need_map;
   sp.src_base = a->src_base; sp.src_stride = a->src_slot_stride;
   sp.no_out = maps_only ? 1 : 0;
-  sp.dual = a->kernel == KDA_KERNEL_TCGEN05;       // a mapped segment as one dual-chain task instead of two tasks
+  // a mapped segment as one dual-chain task instead of two tasks; with output rows that needs the tile-major scratch
+  sp.dual = a->kernel == KDA_KERNEL_TCGEN05 && (maps_only || s->tiles != nullptr);
+  if (sp.dual && !maps_only) {
+    if (!aligned16(s->tiles) || s->n_tiles < 0) return KDA_ERR_ARG;
+    sp.tiles = reinterpret_cast<__nv_bfloat16*>(s->tiles);
+  }
   sp.P = s->P; sp.S_loc = s->S_loc;
   sp.tasks = w.tasks; sp.n_tasks = w.n_tasks; sp.status = a->status;
   cudaError_t e = kda::launch_seg_plan(sp, stream);
@@ -315,6 +320,7 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
   kda::ChunkParams p;
   fill_chunk_params(p, a);
   p.out_aux = reinterpret_cast<__nv_bfloat16*>(s->qt);
+  p.oloc_tile_offset = s->n_tiles * a->H * (long long)(KDA_HEAD_DIM * KDA_CHUNK);
   p.key_first = 0;
   p.tasks = w.tasks;
   p.n_tasks = w.n_tasks;
@@ -344,6 +350,28 @@ int kda_fixup_launch(void* out, const void* qt, int64_t ldo, const float* S_in, 
   cudaError_t e = kda::launch_fixup(reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(qt), ldo,
                                     S_in, reinterpret_cast<const long long*>(seg_t0), reinterpret_cast<const long long*>(seg_t1),
                                     seg_need_map, n_seg, H, reinterpret_cast<cudaStream_t>(stream_));
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
+
+int64_t kda_segment_tiles(const int64_t* seg_t0, const int64_t* seg_t1, int32_t n_seg, int64_t T) {
+  if (!seg_t0 || !seg_t1 || n_seg < 0) return 0;
+  int64_t tiles = 0;
+  for (int i = 0; i < n_seg; i++) {
+    const int64_t a = seg_t0[i] < 0 ? 0 : seg_t0[i], b = seg_t1[i] > T ? T : seg_t1[i];
+    if (b > a) tiles += (b - a + KDA_CHUNK - 1) / KDA_CHUNK;
+  }
+  return tiles;
+}
+
+int kda_fixup_tiles_launch(void* out, const void* tiles, int64_t n_tiles, int64_t ldo, const float* S_in,
+                           const int64_t* seg_t0, const int64_t* seg_t1, const int32_t* seg_need_map, int32_t n_seg,
+                           int32_t H, int64_t T, void* stream_) {
+  if (!out || !tiles || !S_in || !seg_t0 || !seg_t1 || !seg_need_map || n_seg < 1 || H < 1 || n_tiles < 0 || T < 0) return KDA_ERR_ARG;
+  if (!aligned16(out) || !aligned16(tiles) || (ldo & 7) || ldo < (int64_t)H * KDA_HEAD_DIM) return KDA_ERR_ARG;
+  cudaError_t e = kda::launch_fixup_tiles(reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(tiles),
+                                          n_tiles * H * (long long)(KDA_HEAD_DIM * KDA_CHUNK), ldo, S_in,
+                                          reinterpret_cast<const long long*>(seg_t0), reinterpret_cast<const long long*>(seg_t1),
+                                          seg_need_map, n_seg, H, T, reinterpret_cast<cudaStream_t>(stream_));
   return e == cudaSuccess ? KDA_OK : cuda_fail(e);
 }
 
@@ -381,6 +409,7 @@ int kda_prefill_plan_counts(const KdaPrefillArgs* a, int32_t* counts, void* stre
   counts[0] = counts[1] = counts[2] = 0;
   cudaError_t e = cudaMemcpyAsync(counts, w.n_tasks, (pieces > 0 ? 3 : 1) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  counts[0] &= kda::NT_ZERO_FILL - 1;
   return e == cudaSuccess ? KDA_OK : cuda_fail(e);
 }
 

@@ -490,13 +490,14 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_fwd_kernel(const ChunkPa
   const int H = p.H;
   const int rank = blockIdx.x / H, h = blockIdx.x % H;
 
-  if (p.status[0] & 1) {
+  const int nt_word = *p.n_tasks;
+  if (nt_word & NT_ZERO_FILL) {
     // rejected cu_seqlens: every sequence is empty; output rows are zero-filled so nothing is left uninitialised
     const long long rows = p.T * H;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x)
       if (tid < 16) reinterpret_cast<uint4*>(p.out + (r / H) * p.ldo + (r % H) * D)[tid] = make_uint4(0, 0, 0, 0);
   }
-  if (rank >= *p.n_tasks) return;
+  if (rank >= (nt_word & (NT_ZERO_FILL - 1))) return;
   const Task task = p.tasks[rank];
   const int nchunks = (task.len + C - 1) / C;
 

@@ -998,8 +998,12 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
     if (lane == 0) mbar_arrive(x.bar(ch ? B_S_READY_T : B_S_READY));
   }
 
-  __nv_bfloat16* obase0 = ((task.flags & TF_OUT_AUX) ? p.out_aux : p.out) + (long long)x.h * D + v;
-  __nv_bfloat16* obase1 = p.out_aux + (long long)x.h * D + v;
+  // Output of a dual-chain task: TILE-MAJOR scratch, [chunk][head][row v][32 tokens] bf16, Qt tiles at task.ck and the
+  // o_loc tiles `oloc_tile_offset` elements behind them.  A lane owns one row v of the tile and 16 of its tokens, so
+  // its share is 32 contiguous bytes (two 16-byte stores) instead of sixteen 2-byte stores 2 ldo bytes apart: the
+  // tensor-memory warps are the busiest role of a dual task, and the output rows were a quarter of their time.  The
+  // fix-up pass reads the tiles as they are (8 KB contiguous each) and writes the final rows.
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(task.ck) + (size_t)x.h * (D * C) + v * C + 16 * hf;
 #pragma unroll 1
   for (int c = 0; c <= x.nchunks; c++) {
     const bool last = c == x.nchunks;
@@ -1025,8 +1029,7 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
       }
     }
     if (last) break;
-    // ---- output rows of this chunk, chain L then chain Tr
-    const int nvalid = min(C, x.len - c * C);
+    // ---- output tiles of this chunk, chain L then chain Tr
 #pragma unroll 1
     for (int ch = 0; ch < 2; ch++) {
       x.wait(B_O_FULL + ch, (uint32_t)(c & 1), E_EPI);       // one output buffer per chain (see role_mma_dual)
@@ -1038,10 +1041,11 @@ __device__ void role_tmem_dual(const ChunkParams& p, const Task& task, const Ctx
       __syncwarp();
       if (lane == 0) mbar_arrive(x.bar(B_O_EMPTY + ch));
       if (!(task.flags & TF_NO_OUT)) {
-        __nv_bfloat16* orow = (ch ? obase1 : obase0) + (x.t0 + (long long)c * C + 16 * hf) * p.ldo;
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-          if (16 * hf + i < nvalid) orow[(long long)i * p.ldo] = __float2bfloat16_rn(__uint_as_float(o[i]));
+        uint4* dst = reinterpret_cast<uint4*>(tiles + (ch ? 0 : p.oloc_tile_offset) + (size_t)c * p.H * (D * C));
+        dst[0] = make_uint4(pack_bf16(__uint_as_float(o[0]), __uint_as_float(o[1])), pack_bf16(__uint_as_float(o[2]), __uint_as_float(o[3])),
+                            pack_bf16(__uint_as_float(o[4]), __uint_as_float(o[5])), pack_bf16(__uint_as_float(o[6]), __uint_as_float(o[7])));
+        dst[1] = make_uint4(pack_bf16(__uint_as_float(o[8]), __uint_as_float(o[9])), pack_bf16(__uint_as_float(o[10]), __uint_as_float(o[11])),
+                            pack_bf16(__uint_as_float(o[12]), __uint_as_float(o[13])), pack_bf16(__uint_as_float(o[14]), __uint_as_float(o[15])));
       }
     }
   }
@@ -1059,12 +1063,13 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
   // Launched as a programmatic dependent of the planner (its CTAs become resident while the planner still runs): wait
   // here until the planner's writes (status, task table) are visible.  A no-op for an ordinary launch.
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  if (p.status[0] & 1) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
+  const int nt_word = *p.n_tasks;
+  if (nt_word & NT_ZERO_FILL) {   // rejected cu_seqlens: all sequences empty, output rows zero-filled
     const long long rows = p.T * H;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x)
       if (tid < 16) reinterpret_cast<uint4*>(p.out + (r / H) * p.ldo + (r % H) * D)[tid] = make_uint4(0, 0, 0, 0);
   }
-  if (rank >= *p.n_tasks) return;
+  if (rank >= (nt_word & (NT_ZERO_FILL - 1))) return;
   const Task task = p.tasks[rank];
   Ctx x;
   x.smem = smem;

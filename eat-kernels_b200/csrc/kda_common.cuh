@@ -12,6 +12,11 @@ constexpr int HALF = 16;        // sub-chunk: reference exponent taken after tok
 constexpr int STATE_ELEMS = D * D;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// The task count word the planner leaves for the chunk kernels: count in the low bits, plus this bit when cu_seqlens was
+// rejected and the launch has to zero-fill the output rows (one word, so that a CTA without a task exits after a
+// single load: capacity-sized grids are mostly such CTAs).
+constexpr int NT_ZERO_FILL = 1 << 30;
+
 // Task flags
 constexpr uint32_t TF_INIT_ZERO = 1u;      // start from S = 0
 constexpr uint32_t TF_INIT_IDENTITY = 2u;  // start from S = I (transition chain)
@@ -30,7 +35,8 @@ struct __align__(16) Task {
   uint32_t flags;
   const float* src;    // initial state of head 0 (heads 16384 floats apart); unused with TF_INIT_*
   float* dst;          // final state of head 0, or nullptr
-  void* ck;            // first checkpoint row of this run (head 0), or nullptr
+  void* ck;            // first checkpoint row of this run (head 0), or nullptr; TF_DUAL tasks that write output: the
+                       // task's first Qt tile (head 0) in the tile-major scratch (see role_tmem_dual)
   float* dst2;         // TF_DUAL: final state of the transition chain (head 0, always value-first); else unused
 };
 
@@ -42,6 +48,7 @@ struct ChunkParams {
   const void* beta;
   __nv_bfloat16* out;
   __nv_bfloat16* out_aux;
+  long long oloc_tile_offset;  // dual-chain tasks with output: elements from a task's Qt tiles to its o_loc tiles
   long long ldq, ldk, ldv, ldg, ldbeta, ldo;
   const float* A_log;
   const float* dt_bias;

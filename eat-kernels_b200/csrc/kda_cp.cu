@@ -11,6 +11,17 @@
 namespace kda {
 
 // ------------------------------------------------------------------------------------------------ segment tasks
+// Tile-major output scratch of dual-chain tasks: segment i owns ceil(len_i / 32) tiles per head, after those of the
+// segments before it (every segment counts, mapped or not, so that the planner and the fix-up agree without a table).
+__device__ __forceinline__ long long seg_tile0(const long long* t0s, const long long* t1s, long long T, int seg) {
+  long long tiles = 0;
+  for (int j = 0; j < seg; j++) {
+    const long long a = max(0LL, t0s[j]), b = min(T, t1s[j]);
+    if (b > a) tiles += (b - a + C - 1) / C;
+  }
+  return tiles;
+}
+
 __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // see kda_plan_kernel
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n_seg; i += gridDim.x * blockDim.x) {
@@ -26,9 +37,10 @@ __global__ void kda_seg_plan_kernel(const SegPlanParams a) {
       l.flags = TF_INIT_ZERO;
       r.flags = TF_INIT_IDENTITY | TF_V_ZERO | TF_OUT_AUX;
       r.dst = a.P + slot;
-      if (a.dual) {                       // both chains in one task: chain Tr's rows go to the auxiliary output, its map to dst2
-        l.flags |= TF_DUAL;
+      if (a.dual) {                       // both chains in one task: the map of chain Tr goes to dst2, the outputs of both
+        l.flags |= TF_DUAL;               // chains to the tile-major scratch (tiles of the earlier segments come first)
         l.dst2 = a.P + slot;
+        if (a.tiles != nullptr) l.ck = a.tiles + seg_tile0(a.t0, a.t1, a.T, i) * a.H * (D * C);
       }
     } else {
       if (a.src_base != nullptr) l.src = a.src_base + (size_t)i * a.src_stride;
@@ -215,6 +227,147 @@ cudaError_t launch_fixup(__nv_bfloat16* out, const __nv_bfloat16* qt, long long 
   if (split < 1) split = 1;
   if (split > 64) split = 64;
   kda_fixup_kernel<<<(unsigned)(n_seg * H * split), FIX_THREADS, FIX_SMEM, stream>>>(out, qt, ldo, S_in, t0, t1, need_map, n_seg, H, split);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ fix-up over tiles
+// The same pass for the tile-major output of dual-chain tasks: per (segment, head) and 32-token tile, the Qt tile and
+// the o_loc tile are 8 KB contiguous each, [row v or k'][32 tokens] bf16.  out rows = o_loc + Qt applied to bf16(S_in).
+// The Qt tile is the A operand with its rows (tokens) along the contiguous direction, so it is read with transposing
+// ldmatrix; a 16-byte piece (8 tokens of one row) goes to  row * 64 + ((piece ^ ((row >> 1) & 3)) << 4)  in shared
+// memory, which spreads the eight rows of a ldmatrix phase over all banks.  The sums are staged in the row-major
+// layout of the row-wise pass (over the Qt tile, which is dead by then) and leave as whole 256-byte rows.
+__device__ __forceinline__ uint32_t vt_off(int row, int tok) {
+  return (uint32_t)row * 64u + (uint32_t)(((tok >> 3) ^ ((row >> 1) & 3)) << 4) + (uint32_t)(tok & 7) * 2u;
+}
+
+__global__ void __launch_bounds__(FIX_THREADS) kda_fixup_tiles_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ tiles,
+                                                                      long long oloc_tile_offset, long long ldo,
+                                                                      const float* __restrict__ S_in, const long long* __restrict__ t0s,
+                                                                      const long long* __restrict__ t1s, const int* __restrict__ need_map,
+                                                                      int n_seg, int H, long long T, int split) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int slice = blockIdx.x % split;
+  const int h = (blockIdx.x / split) % H;
+  const int seg = blockIdx.x / (split * H);
+  if (seg >= n_seg || !need_map[seg]) return;
+  const long long t0 = max(0LL, t0s[seg]), t1 = min(T, t1s[seg]);
+  if (t1 <= t0) return;
+  const int ntiles = (int)((t1 - t0 + 31) / 32);
+  if (slice >= ntiles) return;
+  const __nv_bfloat16* qt_tiles = tiles + (seg_tile0(t0s, t1s, T, seg) * H + h) * (D * C);
+
+  // entering state -> bf16 [v][k'] tile (row = value index: the B operand with k' contiguous)
+  const float* S = S_in + ((size_t)seg * H + h) * STATE_ELEMS;
+  for (int idx = tid; idx < D * D / 4; idx += FIX_THREADS) {
+    const int row = idx >> 5, c4 = (idx & 31) * 4;
+    const float4 f = *reinterpret_cast<const float4*>(S + row * D + c4);
+    *reinterpret_cast<uint2*>(smem + tile128_off(row, c4)) = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
+  }
+  const uint32_t s_tile = smem_u32(smem);
+  const int g = lane >> 2, t = lane & 3;
+  const int frag_row = 8 * (lane >> 4) + (lane & 7);
+  const int frag_chunk = (lane >> 3) & 1;
+
+  auto issue = [&](int tile, int buf) {
+    const __nv_bfloat16* src = qt_tiles + (size_t)tile * H * (D * C);
+    const uint32_t dst = smem_u32(smem + 32768 + buf * 16384);
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int idx = tid + FIX_THREADS * j, row = idx >> 2, piece = idx & 3;
+      const uint32_t soff = row * 64 + ((piece ^ ((row >> 1) & 3)) << 4);
+      cp_async16(dst + soff, src + idx * 8, 16);
+      cp_async16(dst + 8192 + soff, src + oloc_tile_offset + idx * 8, 16);
+    }
+  };
+  issue(slice, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int tile = slice; tile < ntiles; tile += split, buf ^= 1) {
+    if (tile + split < ntiles) issue(tile + split, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    uint8_t* q_buf = smem + 32768 + buf * 16384;
+    const uint32_t q_tile = smem_u32(q_buf);
+    const uint8_t* o_tile = q_buf + 8192;
+    float acc[2][2][4];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+      for (int b = 0; b < 2; b++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[a][b][c] = 0.0f;
+    // A fragment (16 tokens x 16 k') from the [k'][token] tile: matrix m of the ldmatrix covers tokens 8 (m & 1) ..,
+    // k' 8 (m >> 1) ..; lanes 8 m .. 8 m + 7 give the addresses of its eight k' rows
+    const int a_tok = 8 * ((lane >> 3) & 1), a_k = 8 * (lane >> 4) + (lane & 7);
+#pragma unroll
+    for (int kt = 0; kt < 8; kt++) {
+      uint32_t b[4];
+      ldmatrix_x4(b, s_tile + tile128_off(16 * warp + frag_row, (2 * kt + frag_chunk) * 8));
+#pragma unroll
+      for (int mt = 0; mt < 2; mt++) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, q_tile + vt_off(16 * kt + a_k, 16 * mt + a_tok));
+        mma_bf16(acc[mt][0], a, b[0], b[1]);
+        mma_bf16(acc[mt][1], a, b[2], b[3]);
+      }
+    }
+    // + o_loc (row = value index, token along the row)
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int tok = 16 * mt + g + 8 * half;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const int vv = 16 * warp + 8 * nt + 2 * t;
+          acc[mt][nt][2 * half] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(o_tile + vt_off(vv, tok)));
+          acc[mt][nt][2 * half + 1] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(o_tile + vt_off(vv + 1, tok)));
+        }
+      }
+    __syncthreads();                               // every warp is done with the Qt tile: the sums take its place
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int row = 16 * mt + g + 8 * half;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+          *reinterpret_cast<uint32_t*>(q_buf + tile128_off(row, 16 * warp + 8 * nt + 2 * t)) =
+              pack_bf16(acc[mt][nt][2 * half], acc[mt][nt][2 * half + 1]);
+      }
+    __syncthreads();
+    const long long tok0 = t0 + (long long)tile * 32;
+    const int nvalid = (int)min(32LL, t1 - tok0);
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int idx = tid + FIX_THREADS * j, row = idx >> 4, ch = idx & 15;
+      if (row < nvalid)
+        *reinterpret_cast<uint4*>(out + (tok0 + row) * ldo + (long long)h * D + ch * 8) =
+            *reinterpret_cast<const uint4*>(q_buf + row * 256 + ((ch ^ (row & 7)) << 4));
+    }
+    __syncthreads();
+  }
+}
+
+cudaError_t launch_fixup_tiles(__nv_bfloat16* out, const __nv_bfloat16* tiles, long long oloc_tile_offset, long long ldo,
+                               const float* S_in, const long long* t0, const long long* t1, const int* need_map, int n_seg,
+                               int H, long long T, cudaStream_t stream) {
+  static int attr_dev_mask = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_dev_mask & (1 << (dev & 31)))) {
+    cudaError_t e = cudaFuncSetAttribute(kda_fixup_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FIX_SMEM);
+    if (e != cudaSuccess) return e;
+    attr_dev_mask |= 1 << (dev & 31);
+  }
+  int split = (4 * 148 + n_seg * H - 1) / (n_seg * H);
+  if (split < 1) split = 1;
+  if (split > 64) split = 64;
+  kda_fixup_tiles_kernel<<<(unsigned)(n_seg * H * split), FIX_THREADS, FIX_SMEM, stream>>>(out, tiles, oloc_tile_offset, ldo, S_in, t0, t1,
+                                                                                           need_map, n_seg, H, T, split);
   return cudaGetLastError();
 }
 

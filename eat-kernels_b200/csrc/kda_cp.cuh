@@ -15,6 +15,7 @@ struct SegPlanParams {
   int dual;        // 1: a mapped segment is ONE dual-chain task (tcgen05 kernel only); 0: two tasks, chains L and Tr
   float* P;
   float* S_loc;
+  __nv_bfloat16* tiles;  // dual with output: tile-major scratch (Qt tiles; the o_loc tiles follow at ChunkParams::oloc_tile_offset)
   Task* tasks;     // [2 * n_seg] (dual: n_seg used)
   int* n_tasks;
   int* status;
@@ -25,6 +26,10 @@ cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, flo
                         cudaStream_t stream);
 cudaError_t launch_fixup(__nv_bfloat16* out, const __nv_bfloat16* qt, long long ldo, const float* S_in, const long long* t0,
                          const long long* t1, const int* need_map, int n_seg, int H, cudaStream_t stream);
+// the same pass over the tile-major output of dual-chain tasks: out rows = o_loc tile + Qt tile applied to the entering state
+cudaError_t launch_fixup_tiles(__nv_bfloat16* out, const __nv_bfloat16* tiles, long long oloc_tile_offset, long long ldo,
+                               const float* S_in, const long long* t0, const long long* t1, const int* need_map, int n_seg,
+                               int H, long long T, cudaStream_t stream);
 cudaError_t launch_rows_copy(void* dst, long long dst_row_stride, int dst_is_bf16, const float* src, long long src_row_stride,
                              const int* idx, int n_rows, int H, cudaStream_t stream);
 

@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
       a.tasks[i] = a.tasks_unsorted[srcpos];
     }
     if (tid == 0) {
-      *a.n_tasks = N;
+      *a.n_tasks = N | (noop ? NT_ZERO_FILL : 0);
       if (a.n_tasks_b != nullptr) { *a.n_tasks_b = 0; *a.n_chains = 0; }
     }
   } else {

@@ -14,7 +14,7 @@ NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
 KERNEL_TCGEN05, KERNEL_MMA_SYNC, KERNEL_TCGEN05_TWO_TASK = 0, 1, 2
 MAX_CUT_PIECES = 128
 EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_workspace_bytes_cuts", "kda_prefill_launch", "kda_prefill_plan_counts", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
-           "kda_fixup_launch", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",
+           "kda_fixup_launch", "kda_fixup_tiles_launch", "kda_segment_tiles", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",
            "kda_debug_configure"]
 
 
@@ -48,6 +48,7 @@ class KdaSegmentArgs(C.Structure):
         ("n_seg", C.c_int32),
         ("seg_t0", C.c_void_p), ("seg_t1", C.c_void_p), ("seg_need_map", C.c_void_p),
         ("qt", C.c_void_p), ("P", C.c_void_p), ("S_loc", C.c_void_p),
+        ("tiles", C.c_void_p), ("n_tiles", C.c_int64),
     ]
 
 
@@ -80,6 +81,11 @@ def lib():
         L.kda_fixup_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_int32, C.c_int32, C.c_void_p]
         L.kda_fixup_launch.restype = C.c_int
+        L.kda_fixup_tiles_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]
+        L.kda_fixup_tiles_launch.restype = C.c_int
+        L.kda_segment_tiles.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64]
+        L.kda_segment_tiles.restype = C.c_int64
         L.kda_state_rows_copy.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,
                                           C.c_int32, C.c_void_p]
         L.kda_state_rows_copy.restype = C.c_int

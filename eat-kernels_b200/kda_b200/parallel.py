@@ -16,7 +16,8 @@ chains per piece in one launch, composes its pieces into one map per head, all-g
 fixes the outputs up.  The first piece of rank 0 knows its entering state (the caller's initial state), runs the plain
 chain and contributes the map (P = 0, S_loc = its true end state), which keeps the algebra uniform.
 
-The three compute steps go through the C ABI (kda_segment_launch, kda_scan_launch, kda_fixup_launch).  They are
+The three compute steps go through the C ABI (kda_segment_launch, kda_scan_launch, kda_fixup_tiles_launch or
+kda_fixup_launch).  They are
 grouped in a backend object so that the orchestration (piece boundaries, gather layout, scan order) can be exercised
 on CPU ranks with a stand-in backend supplied by the tests; the package itself ships only the CUDA backend.
 """
@@ -191,6 +192,7 @@ class CudaBackend:
         self.reuse = bool(reuse)
         self._bufs = {}
         self._table_cache = {}
+        self._tiled = (False, 0, 0)
         self.status = None          # int32[4] of the most recent segment launch: [2] != 0 means a wait inside it gave up
 
     def _buf(self, key, shape, dtype, dev, zero=False):
@@ -226,14 +228,23 @@ class CudaBackend:
 
     def segment_maps(self, q, k, v, g, beta, A_log, dt_bias, scale, raw, bounds, need_map, first_state):
         """Runs chain L (and chain Tr where need_map) for the pieces [bounds[i], bounds[i+1]) in one launch.
-        Returns out [1,T,H,128] bf16 (o_loc), qt [1,T,H,128] bf16, P, S_loc [n,H,128,128] fp32 (value-first).
-        On the tcgen05 kernel a mapped piece is ONE dual-chain task per head (both chains over one operand
-        preparation) next to the plain tasks of unmapped pieces; `dual=False` keeps the two-task scheme."""
+        Returns (out, qt, P, S_loc): P, S_loc [n,H,128,128] fp32 (value-first); out [1,T,H,128] bf16; qt the handle that
+        `fixup` takes.  On the tcgen05 kernel a mapped piece is ONE dual-chain task per head (both chains over one operand
+        preparation) next to the plain tasks of unmapped pieces; its o_loc and Qt go TILE-MAJOR into a scratch
+        (`qt` is that scratch; `out` then holds rows only for unmapped pieces until `fixup` has run; `rows_of` gives the
+        row form for inspection).  `dual=False` keeps two tasks per mapped piece with o_loc rows in `out` and Qt rows in
+        `qt` [1,T,H,128]."""
         dev = q.device
         T, H = q.shape[1], q.shape[2]
         n = len(bounds) - 1
+        tiled = self.dual and self.kernel == _cabi.KERNEL_TCGEN05 and any(need_map)
         out = self._buf("out", (1, T, H, D), torch.bfloat16, dev)
-        qt = self._buf("qt", (1, T, H, D), torch.bfloat16, dev)
+        n_tiles = sum(-(-(bounds[i + 1] - bounds[i]) // CHUNK) for i in range(n))
+        if tiled:
+            qt = self._buf("tiles", (2, n_tiles, H, D, CHUNK), torch.bfloat16, dev)      # [0] Qt tiles, [1] o_loc tiles
+        else:
+            qt = self._buf("qt", (1, T, H, D), torch.bfloat16, dev)
+        self._tiled = (tiled, n_tiles, T)
         # (the P of an unmapped piece must read as the zero map; mapped pieces overwrite theirs)
         P = self._buf("P", (n, H, D, D), torch.float32, dev, zero=not all(need_map))
         S_loc = self._buf("S_loc", (n, H, D, D), torch.float32, dev)
@@ -262,9 +273,28 @@ class CudaBackend:
         s.n_seg = n
         s.seg_t0, s.seg_t1, s.seg_need_map = t0.data_ptr(), t1.data_ptr(), nm.data_ptr()
         s.qt, s.P, s.S_loc = qt.data_ptr(), P.data_ptr(), S_loc.data_ptr()
+        if tiled:
+            s.tiles, s.n_tiles = qt.data_ptr(), n_tiles
         _cabi.check(self.lib.kda_segment_launch(C.byref(s), self._stream(dev)), "kda_segment_launch")
         self._keep = (t0, t1, nm, ws, status)       # alive until the stream has consumed them
         return out, qt, P, S_loc
+
+    def rows_of(self, out, qt, bounds, need_map):
+        """(o_loc rows, Qt rows) [1,T,H,128] of the most recent `segment_maps` call, whichever form it wrote (tests)."""
+        if not self._tiled[0]:
+            return out, qt
+        T, H = out.shape[1], out.shape[2]
+        o_rows, q_rows = out.clone(), torch.zeros_like(out)
+        tile = 0
+        for i in range(len(bounds) - 1):
+            t0, t1 = bounds[i], bounds[i + 1]
+            nt = -(-(t1 - t0) // CHUNK)
+            if need_map[i] and nt:
+                for dst, src in ((q_rows, qt[0]), (o_rows, qt[1])):
+                    rows = src[tile:tile + nt].permute(0, 3, 1, 2).reshape(nt * CHUNK, H, D)     # [tile][tok][h][v] -> rows
+                    dst[0, t0:t1] = rows[:t1 - t0]
+            tile += nt
+        return o_rows, q_rows
 
     def scan(self, P, S_loc, S0):
         """S_in[0] = S0 (or 0), S_in[i+1] = S_in[i] @ P[i] + S_loc[i]; returns (S_in [n,H,128,128], S_end [H,128,128])."""
@@ -279,8 +309,13 @@ class CudaBackend:
         dev = out.device
         n, H = len(bounds) - 1, out.shape[2]
         t0, t1, nm = self._tables(bounds, need_map, dev)
-        _cabi.check(self.lib.kda_fixup_launch(out.data_ptr(), qt.data_ptr(), H * D, S_in.data_ptr(), t0.data_ptr(), t1.data_ptr(),
-                                              nm.data_ptr(), n, H, self._stream(dev)), "kda_fixup_launch")
+        tiled, n_tiles, T = getattr(self, "_tiled", (False, 0, 0))
+        if tiled:
+            _cabi.check(self.lib.kda_fixup_tiles_launch(out.data_ptr(), qt.data_ptr(), n_tiles, H * D, S_in.data_ptr(), t0.data_ptr(),
+                                                        t1.data_ptr(), nm.data_ptr(), n, H, T, self._stream(dev)), "kda_fixup_tiles_launch")
+        else:
+            _cabi.check(self.lib.kda_fixup_launch(out.data_ptr(), qt.data_ptr(), H * D, S_in.data_ptr(), t0.data_ptr(), t1.data_ptr(),
+                                                  nm.data_ptr(), n, H, self._stream(dev)), "kda_fixup_launch")
         self._keep2 = (t0, t1, nm)
         return out
 

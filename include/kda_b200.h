@@ -185,7 +185,18 @@ typedef struct KdaSegmentArgs {
                                  rows are written by either chain and base.out may be NULL too */
   float* P;                   /* [n_seg][H][128][128] transition maps, value-first */
   float* S_loc;               /* [n_seg][H][128][128] offsets; for unmapped segments the true end state */
+  void* tiles;                /* KDA_KERNEL_TCGEN05 with output rows: bf16 scratch of 2 * kda_segment_tiles(..) * H * 4096
+                                 elements.  Mapped segments run as dual-chain tasks that write o_loc and Qt TILE-MAJOR
+                                 here ([tile][head][128][32 tokens]; Qt tiles first, the o_loc tiles behind them) instead of
+                                 as rows of base.out / qt; kda_fixup_tiles_launch turns them into the rows of base.out.
+                                 NULL: two single-chain tasks per mapped segment, rows in base.out / qt (as with
+                                 KDA_KERNEL_TCGEN05_TWO_TASK); qt is not written when tiles is given, but must be
+                                 non-NULL to ask for output */
+  int64_t n_tiles;            /* kda_segment_tiles() of the segment tables: where the o_loc tiles start in `tiles` */
 } KdaSegmentArgs;
+
+/* Tiles of 32 tokens the segments [t0[i], t1[i]) take in the tile-major scratch (HOST copies of the tables). */
+int64_t kda_segment_tiles(const int64_t* seg_t0, const int64_t* seg_t1, int32_t n_seg, int64_t T);
 
 int kda_segment_launch(const KdaSegmentArgs* args, void* stream);
 
@@ -198,6 +209,12 @@ int kda_scan_launch(const float* P, const float* S_loc, const float* S0, float* 
  * bf16, as kda/b200/csrc/w3/cp_fix.cu:279-377). */
 int kda_fixup_launch(void* out, const void* qt, int64_t ldo, const float* S_in, const int64_t* seg_t0,
                      const int64_t* seg_t1, const int32_t* seg_need_map, int32_t n_seg, int32_t H, void* stream);
+
+/* The same pass for a segment launch that wrote tile-major scratch (KdaSegmentArgs::tiles): out rows of the mapped
+ * segments = o_loc tile + S_in[i] applied to the Qt tile; `tiles` and `n_tiles` as given to / sized for that launch. */
+int kda_fixup_tiles_launch(void* out, const void* tiles, int64_t n_tiles, int64_t ldo, const float* S_in,
+                           const int64_t* seg_t0, const int64_t* seg_t1, const int32_t* seg_need_map, int32_t n_seg,
+                           int32_t H, int64_t T, void* stream);
 
 /* dst row i <- src row idx[i] (64 KB fp32 rows per head), optionally rounding to bf16 (round to nearest even).
  * Rows are [H][128][128]; strides in elements of the respective type. */

@@ -62,8 +62,10 @@ def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow, plain
     res = {}
     for dual in (True, False):
         be = parallel.CudaBackend(dual=dual)
-        res[dual] = [t.clone() for t in be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need,
-                                                        init if plain_first else None)]
+        out, qt, P, S_loc = be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need,
+                                            init if plain_first else None)
+        o_rows, q_rows = be.rows_of(out, qt, bounds, need)       # the dual-chain tasks write tiles: bring them to rows
+        res[dual] = [t.clone() for t in (o_rows, q_rows, P, S_loc)]
         torch.cuda.synchronize()
         assert be.kernel_error() == 0
     t_map = bounds[1] if plain_first else 0          # Qt rows exist for mapped tokens only
