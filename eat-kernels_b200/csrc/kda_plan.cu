@@ -25,7 +25,7 @@ constexpr int CUT_MAX_SEQS = 1024;       // sequences a cut plan is made for (be
 constexpr int N_CAND = 9;                // candidate piece lengths
 constexpr int MIN_PIECE_CHUNKS = 16;     // shorter pieces drown in the per-task cost
 constexpr int TASK_OVERHEAD = 3;         // start / end of a task, in chunk steps
-constexpr int DUAL_X8 = 13;              // a dual-chain chunk step costs 13 / 8 single-chain ones (measured 1.62)
+constexpr int DUAL_X8 = 9;               // a dual-chain chunk step without output rows costs 9 / 8 single-chain ones (measured 1.05-1.1)
 
 // chunk steps of the map of one piece of lp chunks: one dual-chain task, or two single-chain tasks
 __device__ __forceinline__ long long map_task_cost(int lp, int dual) {

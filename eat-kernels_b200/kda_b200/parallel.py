@@ -86,8 +86,8 @@ def plan_bounds(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fi
     return list(_plan(T, H, first_rank, n_sms, max_pieces, task_overhead, fixup_steps_per_chunk_head)[0])
 
 
-DUAL_COST = 1.62     # a dual-chain chunk step in units of a single-chain one (measured inside the 131072-token segment
-                     # launches: 4.58 us against 2.82 us per chunk)
+DUAL_COST = 1.40     # a dual-chain chunk step (with its two output tiles) in units of a single-chain one (measured inside the
+                     # 131072-token segment launches: 3.44 us against 2.47 us per chunk at 1.97 GHz)
 
 
 @functools.lru_cache(maxsize=256)        # the search costs milliseconds on the host; layouts repeat call after call
@@ -103,7 +103,7 @@ def _plan(T, H, first_rank, n_sms=148, max_pieces=8, task_overhead=3.0, fixup_st
     if nch <= 1:
         return [0, T], (float(nch) + task_overhead, 0.0)
     best, best_cost = [0, nch], None
-    firsts = sorted({nch} | {max(1, int(nch * f / 16)) for f in range(1, 16)}) if first_rank else [0]
+    firsts = sorted({nch} | {max(1, int(nch * f / 32)) for f in range(1, 32)}) if first_rank else [0]
     for c_first in firsts:
         rest = nch - c_first
         for m in range(0, max_pieces + 1):
