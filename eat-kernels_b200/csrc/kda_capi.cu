@@ -398,7 +398,7 @@ const char* kda_error_string(int code) {
 
 size_t kda_abi_struct_bytes(int which) { return which == 0 ? sizeof(KdaPrefillArgs) : (which == 1 ? sizeof(KdaSegmentArgs) : 0); }
 
-const char* kda_version(void) { return "kda_b200 3 sm_100a"; }
+const char* kda_version(void) { return "kda_b200 4 sm_100a"; }
 
 int kda_prefill_plan_counts(const KdaPrefillArgs* a, int32_t* counts, void* stream_) {
   if (a == nullptr || counts == nullptr || a->workspace == nullptr || a->H <= 0 || a->N < 1) return KDA_ERR_ARG;

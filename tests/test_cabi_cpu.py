@@ -51,6 +51,21 @@ def test_null_arguments_are_rejected_without_a_device(lib):
     assert lib.kda_prefill_launch(ctypes.byref(a), None) == -1        # no workspace / status
     assert lib.kda_scan_launch(None, None, None, None, None, 1, 1, None) == -1
     assert lib.kda_state_rows_copy(None, 0, 0, None, 0, None, 1, 1, None) == -1
+    assert lib.kda_fixup_tiles_launch(None, None, 0, 0, None, None, None, None, 1, 1, 0, None) == -1
+
+
+def test_segment_tiles_counts_tiles_of_32_tokens_per_segment(lib):
+    """Host helper that sizes the tile-major scratch of a segment launch: every segment rounds up on its own, tables
+    are clamped to [0, T] as the device planner clamps them."""
+    def tiles(t0, t1, T):
+        a = (ctypes.c_int64 * len(t0))(*t0)
+        b = (ctypes.c_int64 * len(t1))(*t1)
+        return lib.kda_segment_tiles(a, b, len(t0), T)
+    assert tiles([0, 33, 64], [33, 64, 1000], 1000) == 2 + 1 + 30
+    assert tiles([0], [131072], 131072) == 4096
+    assert tiles([-5, 10], [10, 99], 40) == 1 + 1          # clamped: [0, 10) and [10, 40)
+    assert tiles([7], [7], 100) == 0
+    assert lib.kda_segment_tiles(None, None, 3, 10) == 0
 
 
 def test_host_argument_contract():

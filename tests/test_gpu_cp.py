@@ -81,6 +81,29 @@ def test_dual_chain_segments_match_two_task_segments(kda, H, bounds, slow, plain
     ko.check_close(S.float()[None], fin.cpu(), f"state through the dual-chain maps (H={H}, bounds={bounds})", 6e-3)
 
 
+@pytest.mark.parametrize("H,bounds", [(3, [0, 33, 64, 1000, 2047]), (5, [0, 1, 40, 41]), (8, [0, 512, 1024])])
+def test_fixup_over_tiles_matches_fixup_over_rows(kda, H, bounds):
+    """The two forms of the fix-up (tile-major scratch of dual-chain tasks, rows of the two-task scheme) give the same
+    output rows bit for bit, also for pieces that do not start on a multiple of 32 tokens, and they match the plain
+    call within the tolerance."""
+    from kda_b200 import parallel
+    T = bounds[-1]
+    inputs = ko.make_inputs_raw(H, [T], 90 + H)
+    q, k, v, g, beta, A_log, dt_bias, scale, init, _ = to_dev(inputs)
+    need = [0] + [1] * (len(bounds) - 2)
+    outs = {}
+    for dual in (True, False):
+        be = parallel.CudaBackend(dual=dual)
+        out, qt, P, S_loc = be.segment_maps(q, k, v, g, beta, A_log, dt_bias, scale, True, bounds, need, init)
+        S_in, _ = be.scan(P, S_loc, None)
+        outs[dual] = be.fixup(out, qt, S_in, bounds, need).clone()
+        torch.cuda.synchronize()
+        assert be.kernel_error() == 0
+    assert torch.equal(outs[True], outs[False]), f"tile and row forms of the fix-up differ (H={H}, bounds={bounds})"
+    o2, _ = kda.run(q, k, v, g, beta, A_log, dt_bias, scale, init, max_cut_pieces=0)
+    ko.check_close(outs[True].cpu(), o2.cpu(), f"fix-up over tiles vs the plain call (H={H}, bounds={bounds})", 6e-3)
+
+
 def test_scan_matches_fp64(kda):
     from kda_b200 import parallel
     be = parallel.CudaBackend()
