@@ -50,4 +50,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of the reference repository>")
+    main(sys.argv[1])
