@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) kda_plan_kernel(const PlanPar
 
   // ---- cuts.  A long sequence is a serial chain of chunks on one SM per head; when such chains, not the total work,
   // bound the launch (few heads per GPU, one long request among short ones), cutting them into pieces of `lp` chunks
-  // shortens the launch although a cut sequence costs about three times its chunks (see PlanParams).  The piece length
+  // shortens the launch although a cut sequence costs about twice its chunks (see PlanParams).  The piece length
   // is chosen among "the longest sequence in 2, 3, 4, 6, ... pieces" by a cost model in chunk steps, against not
   // cutting at all.  Pieces are multiples of the checkpoint interval, so every checkpoint row is written by the piece
   // that holds its token.  Function of the reference's host planners (kda/b200/csrc/w3/base/kernel.py:389-444,482-532)
