@@ -339,7 +339,14 @@ int kda_segment_launch(const KdaSegmentArgs* s, void* stream_) {
 int kda_scan_launch(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int32_t n_seg,
                     int32_t H, void* stream_) {
   if (!P || !S_loc || !S_in || n_seg < 1 || H < 1) return KDA_ERR_ARG;
-  cudaError_t e = kda::launch_scan(P, S_loc, S0, S_in, S_end, n_seg, H, reinterpret_cast<cudaStream_t>(stream_));
+  cudaError_t e = kda::launch_scan(P, S_loc, S0, S_in, S_end, n_seg, H, 0, reinterpret_cast<cudaStream_t>(stream_));
+  return e == cudaSuccess ? KDA_OK : cuda_fail(e);
+}
+
+int kda_scan_strided_launch(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int32_t n_seg,
+                            int32_t H, int64_t map_stride, void* stream_) {
+  if (!P || !S_loc || !S_in || n_seg < 1 || H < 1 || map_stride < (int64_t)H * kda::STATE_ELEMS || (map_stride & 3)) return KDA_ERR_ARG;
+  cudaError_t e = kda::launch_scan(P, S_loc, S0, S_in, S_end, n_seg, H, map_stride, reinterpret_cast<cudaStream_t>(stream_));
   return e == cudaSuccess ? KDA_OK : cuda_fail(e);
 }
 

@@ -74,12 +74,12 @@ cudaError_t launch_seg_plan(const SegPlanParams& a, cudaStream_t stream) {
 // value rows of one head through the whole chain in fp32 as register tiles (kda_scan_tile.cuh).
 __global__ void __launch_bounds__(ST_THREADS) kda_scan_kernel(const float* __restrict__ P, const float* __restrict__ S_loc,
                                                               const float* __restrict__ S0, float* __restrict__ S_in,
-                                                              float* __restrict__ S_end, int n_seg, int H) {
+                                                              float* __restrict__ S_end, int n_seg, int H, long long map_stride) {
   __shared__ __align__(16) ScanSmem sm;
   const int h = blockIdx.y, tid = threadIdx.x;
   const int r0 = blockIdx.x * ST_ROWS + 4 * (tid >> 5), c0 = 4 * (tid & 31);
   const size_t head_off = (size_t)h * STATE_ELEMS;
-  const size_t seg_stride = (size_t)H * STATE_ELEMS;
+  const size_t seg_stride = (size_t)H * STATE_ELEMS;      // of S_in; the maps may lie further apart (map_stride)
   float cur[4][4];
   if (S0 != nullptr) {
     scan_tile_load(cur, S0 + head_off, r0, c0, 1);
@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(ST_THREADS) kda_scan_kernel(const float* __res
   for (int i = 0; i < n_seg; i++) {
     scan_tile_store(cur, S_in + i * seg_stride + head_off, r0, c0, 1);
     float acc[4][4];
-    scan_tile_load(acc, S_loc + i * seg_stride + head_off, r0, c0, 1);
-    scan_tile_step(acc, cur, P + i * seg_stride + head_off, sm, tid);
+    scan_tile_load(acc, S_loc + (size_t)i * map_stride + head_off, r0, c0, 1);
+    scan_tile_step(acc, cur, P + (size_t)i * map_stride + head_off, sm, tid);
 #pragma unroll
     for (int a = 0; a < 4; a++)
 #pragma unroll
@@ -103,9 +103,10 @@ __global__ void __launch_bounds__(ST_THREADS) kda_scan_kernel(const float* __res
 }
 
 cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int n_seg, int H,
-                        cudaStream_t stream) {
+                        long long map_stride, cudaStream_t stream) {
   dim3 grid(D / ST_ROWS, H);
-  kda_scan_kernel<<<grid, ST_THREADS, 0, stream>>>(P, S_loc, S0, S_in, S_end, n_seg, H);
+  kda_scan_kernel<<<grid, ST_THREADS, 0, stream>>>(P, S_loc, S0, S_in, S_end, n_seg, H,
+                                                   map_stride > 0 ? map_stride : (long long)H * STATE_ELEMS);
   return cudaGetLastError();
 }
 

@@ -22,8 +22,9 @@ struct SegPlanParams {
 };
 
 cudaError_t launch_seg_plan(const SegPlanParams& a, cudaStream_t stream);
+// map_stride: floats between consecutive maps of P and of S_loc (0 = H * 16384, i.e. packed)
 cudaError_t launch_scan(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int n_seg, int H,
-                        cudaStream_t stream);
+                        long long map_stride, cudaStream_t stream);
 cudaError_t launch_fixup(__nv_bfloat16* out, const __nv_bfloat16* qt, long long ldo, const float* S_in, const long long* t0,
                          const long long* t1, const int* need_map, int n_seg, int H, cudaStream_t stream);
 // the same pass over the tile-major output of dual-chain tasks: out rows = o_loc tile + Qt tile applied to the entering state

@@ -13,7 +13,7 @@ STATE_VALUE_FIRST, STATE_KEY_FIRST = 0, 1
 NOALLOC_MAX_SEQS, NOALLOC_MAX_HEADS = 64, 16
 KERNEL_TCGEN05, KERNEL_MMA_SYNC, KERNEL_TCGEN05_TWO_TASK = 0, 1, 2
 MAX_CUT_PIECES = 128
-EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_workspace_bytes_cuts", "kda_prefill_launch", "kda_prefill_plan_counts", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch",
+EXPORTS = ["kda_prefill_workspace_bytes", "kda_prefill_workspace_bytes_cuts", "kda_prefill_launch", "kda_prefill_plan_counts", "kda_prefill_launch_noalloc", "kda_segment_launch", "kda_scan_launch", "kda_scan_strided_launch",
            "kda_fixup_launch", "kda_fixup_tiles_launch", "kda_segment_tiles", "kda_state_rows_copy", "kda_error_string", "kda_abi_struct_bytes", "kda_version",
            "kda_debug_configure"]
 
@@ -78,6 +78,9 @@ def lib():
         L.kda_scan_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                       C.c_void_p]
         L.kda_scan_launch.restype = C.c_int
+        L.kda_scan_strided_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                              C.c_int64, C.c_void_p]
+        L.kda_scan_strided_launch.restype = C.c_int
         L.kda_fixup_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_int32, C.c_int32, C.c_void_p]
         L.kda_fixup_launch.restype = C.c_int

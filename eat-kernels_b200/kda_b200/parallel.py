@@ -301,8 +301,15 @@ class CudaBackend:
         n, H = P.shape[0], P.shape[1]
         S_in = self._buf(("S_in", P.data_ptr()), tuple(S_loc.shape), torch.float32, P.device)
         S_end = self._buf(("S_end", P.data_ptr()), (H, D, D), torch.float32, P.device)
-        _cabi.check(self.lib.kda_scan_launch(P.data_ptr(), S_loc.data_ptr(), None if S0 is None else S0.data_ptr(),
-                                             S_in.data_ptr(), S_end.data_ptr(), n, H, self._stream(P.device)), "kda_scan_launch")
+        s0 = None if S0 is None else S0.data_ptr()
+        if n > 1 and P.stride(0) != H * D * D:
+            # maps that lie apart (the two halves of one gathered [rank][2][H][128][128] buffer)
+            assert P.stride(0) == S_loc.stride(0) and P[0].is_contiguous() and S_loc[0].is_contiguous()
+            _cabi.check(self.lib.kda_scan_strided_launch(P.data_ptr(), S_loc.data_ptr(), s0, S_in.data_ptr(), S_end.data_ptr(), n, H,
+                                                         P.stride(0), self._stream(P.device)), "kda_scan_strided_launch")
+        else:
+            _cabi.check(self.lib.kda_scan_launch(P.data_ptr(), S_loc.data_ptr(), s0, S_in.data_ptr(), S_end.data_ptr(), n, H,
+                                                 self._stream(P.device)), "kda_scan_launch")
         return S_in, S_end
 
     def fixup(self, out, qt, S_in, bounds, need_map):
@@ -495,13 +502,14 @@ def context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, initial_st
     P_rank, L_rank = compose_rank_map(backend, P, S_loc, first_is_zero=not need_map[0])
     mark("maps")
     if world > 1:
-        # two gathers straight into the layout the scan reads ([rank][H][128][128] each): no stacking, no copies
+        # ONE gather of the (P, S_loc) pair of every rank; the scan reads the two halves of the gathered buffer in place
         mk = backend._buf if hasattr(backend, "_buf") else (lambda key, shape, dt, dev, zero=False: torch.empty(shape, dtype=dt, device=dev))
-        gP = mk("gather_P", (world, H, D, D), P_rank.dtype, P_rank.device)
-        gL = mk("gather_L", (world, H, D, D), L_rank.dtype, L_rank.device)
-        dist.all_gather_into_tensor(gP.view(world * H, D, D), P_rank.contiguous(), group=group)
-        dist.all_gather_into_tensor(gL.view(world * H, D, D), L_rank.contiguous(), group=group)
-        S_in_ranks, S_final = backend.scan(gP, gL, None)
+        pair = mk("pair", (2, H, D, D), P_rank.dtype, P_rank.device)
+        pair[0].copy_(P_rank)
+        pair[1].copy_(L_rank)
+        gathered = mk("gather", (world, 2, H, D, D), P_rank.dtype, P_rank.device)
+        dist.all_gather_into_tensor(gathered.view(world * 2 * H, D, D), pair.view(2 * H, D, D), group=group)
+        S_in_ranks, S_final = backend.scan(gathered[:, 0], gathered[:, 1], None)
         S_enter = S_in_ranks[rank]
     else:
         S_enter = None

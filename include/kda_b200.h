@@ -205,6 +205,12 @@ int kda_segment_launch(const KdaSegmentArgs* args, void* stream);
 int kda_scan_launch(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int32_t n_seg,
                     int32_t H, void* stream);
 
+/* The same with the maps `map_stride` floats apart (>= H * 16384, a multiple of 4) instead of packed: P and S_loc may then
+ * be the two halves of one buffer [n_seg][2][H][128][128], which is what ONE all-gather of per-rank (P, S_loc) pairs
+ * delivers.  S_in stays packed. */
+int kda_scan_strided_launch(const float* P, const float* S_loc, const float* S0, float* S_in, float* S_end, int32_t n_seg,
+                            int32_t H, int64_t map_stride, void* stream);
+
 /* out rows of segment i += S_in[i] applied to Qt rows (bf16 tensor-core product with the entering state rounded to
  * bf16, as kda/b200/csrc/w3/cp_fix.cu:279-377). */
 int kda_fixup_launch(void* out, const void* qt, int64_t ldo, const float* S_in, const int64_t* seg_t0,

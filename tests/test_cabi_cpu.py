@@ -50,6 +50,7 @@ def test_null_arguments_are_rejected_without_a_device(lib):
     a.H, a.N, a.T = 4, 1, 0
     assert lib.kda_prefill_launch(ctypes.byref(a), None) == -1        # no workspace / status
     assert lib.kda_scan_launch(None, None, None, None, None, 1, 1, None) == -1
+    assert lib.kda_scan_strided_launch(None, None, None, None, None, 1, 1, 0, None) == -1
     assert lib.kda_state_rows_copy(None, 0, 0, None, 0, None, 1, 1, None) == -1
     assert lib.kda_fixup_tiles_launch(None, None, 0, 0, None, None, None, None, 1, 1, 0, None) == -1
 

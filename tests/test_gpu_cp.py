@@ -120,6 +120,22 @@ def test_scan_matches_fp64(kda):
     assert torch.allclose(S_end.cpu().double(), cur, rtol=1e-4, atol=1e-4)
 
 
+def test_scan_over_one_gathered_buffer_matches_the_packed_scan(kda):
+    """Maps that lie apart (the two halves of one [n][2][H][128][128] buffer, as one all-gather of (P, S_loc) pairs
+    delivers them) scan to the same bits as packed maps."""
+    from kda_b200 import parallel
+    be = parallel.CudaBackend()
+    gen = torch.Generator().manual_seed(6)
+    n, H = 4, 5
+    both = torch.randn(n, 2, H, D, D, generator=gen).to(DEV)
+    both[:, 0] *= 0.08
+    S0 = torch.randn(H, D, D, generator=gen).to(DEV)
+    a_in, a_end = [t.clone() for t in be.scan(both[:, 0].contiguous(), both[:, 1].contiguous(), S0)]
+    b_in, b_end = be.scan(both[:, 0], both[:, 1], S0)
+    torch.cuda.synchronize()
+    assert torch.equal(a_in, b_in) and torch.equal(a_end, b_end)
+
+
 def test_state_rows_copy(kda):
     from kda_b200 import _cabi
     lib = _cabi.lib()
