@@ -42,7 +42,7 @@ METRIC = "KDA prefill tokens/s (H=64,K=V=128 varlen)"
 # dram__bytes_read.sum + dram__bytes_write.sum of kda_chunk_umma_kernel per token-head, taken from one ncu capture of
 # `bench.py --small` (DRAM traffic grows in proportion to token-heads: the kernel streams every operand once).  A
 # constant from that capture, not a live measurement: counters cannot be read inside a timed run.
-NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1701.6
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = 1696.9
 
 
 def workload_lengths(seed=2):
