@@ -104,6 +104,36 @@ def test_fixup_over_tiles_matches_fixup_over_rows(kda, H, bounds):
     ko.check_close(outs[True].cpu(), o2.cpu(), f"fix-up over tiles vs the plain call (H={H}, bounds={bounds})", 6e-3)
 
 
+def test_context_parallel_call_replays_under_a_cuda_graph(kda):
+    """With a reusing backend the context-parallel call allocates nothing after its first run, synchronises nowhere and
+    reads its inputs where they lie: captured once, replayed after the inputs were refilled in place, it gives the
+    result of the refilled inputs."""
+    from kda_b200 import parallel
+    H, T = 6, 4096
+    be = parallel.CudaBackend(reuse=True)
+    data = [to_dev(ko.make_inputs_raw(H, [T], seed)) for seed in (61, 62)]
+    q, k, v, g, beta, A_log, dt_bias, scale, init, _ = [t.clone() if torch.is_tensor(t) else t for t in data[0]]
+
+    def call():
+        return parallel.context_parallel_prefill(q, k, v, g, beta, A_log, dt_bias, scale, init, pieces=4, backend=be)
+
+    for _ in range(2):
+        call()                                    # warm-up: buffers, tables, plan
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, fin = call()
+    for src in (data[1], data[0]):
+        for dst, t in zip((q, k, v, g, beta, A_log, dt_bias, init), (*src[:7], src[8])):
+            dst.copy_(t)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert be.kernel_error() == 0
+        o2, f2 = kda.run(q, k, v, g, beta, A_log, dt_bias, scale, init, max_cut_pieces=0)
+        ko.check_close(out.cpu(), o2.cpu(), "graph replay of the context-parallel call (output)", 6e-3)
+        ko.check_close(fin.cpu(), f2.cpu(), "graph replay of the context-parallel call (state)", 6e-3)
+
+
 def test_scan_matches_fp64(kda):
     from kda_b200 import parallel
     be = parallel.CudaBackend()
