@@ -1114,29 +1114,21 @@ __global__ void __launch_bounds__(THREADS, 1) kda_chunk_umma_kernel(const ChunkP
     *x.abort_flag = 0;
     *range_flag = 0;
     *reinterpret_cast<volatile unsigned long long*>(smem + OFF_MISC + 16) = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
-    for (int i = 0; i < 2; i++) {
-      mbar_init(x.bar(B_G_FULL + i), 1);
-      mbar_init(x.bar(B_G_EMPTY + i), PREP_WARPS);
-      mbar_init(x.bar(B_QK_FULL + i), 1);
-      mbar_init(x.bar(B_QK_EMPTY + i), PREP_WARPS);
+  }
+  if (warp == W_INV0) {
+    // One lane per barrier (the issuer warp allocates tensor memory meanwhile): a task of one or two chunks notices the
+    // forty serial initialisations.  Arrival counts: the eight warps of a preparation group or the eight tensor-memory
+    // warps where a whole group signals, four for the L tile (half a group), one everywhere else.
+    constexpr unsigned long long EIGHT = (3ull << B_G_EMPTY) | (3ull << B_P1_FULL) | (3ull << B_O_EMPTY) | (1ull << B_S_READY) |
+                                         (3ull << B_QK_EMPTY) | (1ull << B_S_READY_T);
+    static_assert(PREP_WARPS == 8, "arrival counts of the group barriers");
+    for (int i = lane; i < NUM_BARS; i += 32) {
+      int count = ((EIGHT >> i) & 1ull) ? 8 : 1;
+      if (i == B_L_FULL || i == B_L_FULL + 1) count = PREP_WARPS / 2;
       // diagnostic switch: the v barriers expect one arrival more than they will ever get, so their waiters give up
-      mbar_init(x.bar(B_V_FULL + i), (p.debug_flags & DBG_STALL_V_STREAM) ? 2 : 1);
-      mbar_init(x.bar(B_KDQD_EMPTY + i), 1);
-      mbar_init(x.bar(B_CONS_EMPTY + i), 1);
-      mbar_init(x.bar(B_P1_FULL + i), PREP_WARPS);
-      mbar_init(x.bar(B_INV_FULL + i), 1);
-      mbar_init(x.bar(B_L_FULL + i), PREP_WARPS / 2);
-      mbar_init(x.bar(B_V_EMPTY + i), 1);
-      mbar_init(x.bar(B_L_EMPTY + i), 1);
-      mbar_init(x.bar(B_O_FULL + i), 1);
-      mbar_init(x.bar(B_O_EMPTY + i), 8);
+      if ((i == B_V_FULL || i == B_V_FULL + 1) && (p.debug_flags & DBG_STALL_V_STREAM)) count = 2;
+      mbar_init(x.bar(i), count);
     }
-    mbar_init(x.bar(B_MMA1_DONE), 1);
-    mbar_init(x.bar(B_S_READY), 8);
-    mbar_init(x.bar(B_MMA1_DONE_T), 1);
-    mbar_init(x.bar(B_S_READY_T), 8);
-    mbar_init(x.bar(B_DRAIN), 1);
-    for (int i = 0; i < 8; i++) mbar_init(x.bar(B_TOT + i), 1);
     fence_barrier_init();
   }
   if (warp == W_MMA) {
